@@ -1,0 +1,261 @@
+/*
+ * lemoq_b200 - C ABI of the B200 (sm_100a) kernels for the LeanMoE-Quant batch-1
+ * decode step.
+ *
+ * Conventions shared by every entry point
+ *   - plain C: device pointers, sizes and a CUDA stream handle (`cudaStream_t`
+ *     passed as `void*`; NULL = the legacy default stream);
+ *   - no allocation, no synchronisation, no host<->device copies: work is only
+ *     enqueued on `stream`, so every call is legal under stream capture;
+ *   - tensors are contiguous unless a stride argument says otherwise; weight,
+ *     cache and activation base pointers must be 16-byte aligned;
+ *   - return value: LEMOQ_OK, or an error code with a message available from
+ *     lemoq_last_error() (thread-local).  LEMOQ_ERR_INVALID maps to the
+ *     reference's ValueError, LEMOQ_ERR_UNSUPPORTED to NotImplementedError and
+ *     LEMOQ_ERR_CUDA to RuntimeError;
+ *   - "ref:" lines name the reference interface (file:line inside the
+ *     LeanMoE-Quant tree) that the entry point replaces.
+ *
+ * Data types: activations, norm weights, router weights, scales and caches are
+ * IEEE fp16; weight and KV codes are int8; expert ids are int64; positions are
+ * int64 (`cache_position`) and the filled length is int32, both read from
+ * device memory so one captured launch serves every step.
+ */
+#ifndef LEMOQ_B200_H
+#define LEMOQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LEMOQ_API __attribute__((visibility("default")))
+#else
+#define LEMOQ_API
+#endif
+
+#define LEMOQ_OK 0
+#define LEMOQ_ERR_INVALID 1
+#define LEMOQ_ERR_UNSUPPORTED 2
+#define LEMOQ_ERR_CUDA 3
+
+#define LEMOQ_DTYPE_F16 0
+#define LEMOQ_DTYPE_F32 1
+
+/* Library / build identification and the last error message of this thread. */
+LEMOQ_API const char* lemoq_version(void);
+LEMOQ_API const char* lemoq_last_error(void);
+
+/* ---------------------------------------------------------------------------
+ * Weight quantisation: per-row, per-group symmetric RTN to int8.
+ * ref: src/lemoq/quant/rtn.py:38 (quantize_rtn, symmetric 8-bit branch),
+ *      src/lemoq/kernels/moe_grouped_quant.py:191 (quantize_fused_experts),
+ *      src/lemoq/quant/linear.py:253 (QuantLinear.__init__: fp16 scale buffer).
+ * w: (rows, in_features) fp16 or fp32 (w_dtype); in_features % group_size == 0.
+ * codes: (rows, in_features) int8; scale: (rows, in_features/group_size) fp16.
+ */
+LEMOQ_API int lemoq_rtn_quantize_w8(const void* w, int w_dtype, int64_t rows, int in_features, int group_size,
+                          int8_t* codes, void* scale, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Dense W8 dequant GEMV: y[m, n] = sum_k x[m, k] * codes[n, k] * scale[n, k/g].
+ * ref: src/lemoq/kernels/_dequant_triton.py:155 (dequant_gemm_fused, symmetric
+ *      8-bit), called from src/lemoq/quant/linear.py:446 (QuantLinear fused arm)
+ *      and src/lemoq/kernels/packed_qkv.py:78 (PackedQKV.project).
+ * x: (M, K) fp16; codes: (N, K) int8; scale: (N, K/g) fp16; y: (M, N) fp16 or
+ * fp32 (out_dtype).  K % group_size == 0, group_size % 16 == 0, K <= 8192.
+ */
+LEMOQ_API int lemoq_dequant_gemv_w8(const void* x, int M, const int8_t* codes, const void* scale, int N, int K,
+                          int group_size, void* y, int out_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * RMSNorm, HF-OLMoE rounding: y = fp16(x * rsqrt(mean(x^2) + eps)) * w (fp16 mul).
+ * ref: src/lemoq/kernels/rmsnorm.py:102 (rms_norm_fused).
+ * x, y: (rows, H) fp16; w: (H,) fp16.  H % 8 == 0, H <= 8192.
+ */
+LEMOQ_API int lemoq_rms_norm(const void* x, const void* w, void* y, int64_t rows, int H, float eps, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Half-split RoPE on the decode q and k rows: out = x*cos + rotate_half(x)*sin in
+ * fp32, one rounding to fp16.
+ * ref: src/lemoq/kernels/rope.py:160 (apply_rotary_pos_emb_fused).
+ * q: heads_q rows of D fp16, row h at q + h*q_head_stride (elements); likewise k.
+ * cos, sin: (D,) fp16.  q_out/k_out: contiguous (heads, D).
+ */
+LEMOQ_API int lemoq_rope_qk(const void* q, int64_t q_head_stride, int heads_q, const void* k, int64_t k_head_stride,
+                  int heads_k, const void* cos, const void* sin, int D, void* q_out, void* k_out, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * KV direct write: bit copy of the new (1,H,1,D) K and V rows into the static
+ * fp16 cache (1,H,max_len,D) at slot *pos; no other slot is touched.
+ * ref: src/lemoq/kernels/kv_direct.py:110 (kv_direct_write),
+ *      contract src/lemoq/kernels/kv_write.py:28 (write_kv_slot).
+ * pos: device int64 scalar.  A position outside [0, max_len) writes nothing and
+ * sets *err_flag (device int32, may be NULL) to 1.
+ */
+LEMOQ_API int lemoq_kv_direct_write(const void* k_row, const void* v_row, int64_t src_head_stride, void* k_cache,
+                          void* v_cache, const int64_t* pos, int heads, int max_len, int D, int* err_flag,
+                          void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Per-token symmetric int8 KV quantisation of the new K and V rows into the
+ * int8 mirror cache at slot *pos: amax/127 in fp32 (1.0 for a zero row), true
+ * division, round half to even, clamp to +-127, scale stored as fp16.
+ * ref: src/lemoq/kernels/kv_int8.py:219 (kv_int8_cache_write); with pos == NULL
+ *      and S == 1 it is src/lemoq/kernels/kv_int8.py:314 (kv_int8_write).
+ * k_row, v_row: (H, D) fp16 contiguous; kc, vc: (H, S, D) int8; ks, vs: (H, S) fp16.
+ */
+LEMOQ_API int lemoq_kv_int8_cache_write(const void* k_row, const void* v_row, int8_t* kc, void* ks, int8_t* vc, void* vs,
+                              const int64_t* pos, int heads, int S, int D, int* err_flag, void* stream);
+
+/* Bulk quantisation of a whole fp16 cache into the mirror; slots at or beyond
+ * `filled` get code 0 / scale 1 (filled < 0 quantises every slot).
+ * ref: src/lemoq/kernels/kv_int8.py:127 (kv_int8_bulk_quantize).
+ */
+LEMOQ_API int lemoq_kv_int8_bulk_quantize(const void* keys, const void* values, int8_t* kc, void* ks, int8_t* vc, void* vs,
+                                int heads, int S, int D, int filled, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Split-KV decode attention over positions [0, *filled): per-split online softmax
+ * (base 2), partials (m, l, acc[D]) in fp32, deterministic fixed-order merge done
+ * by the last block of each head; *filled == 0 gives zeros.
+ * ref: src/lemoq/kernels/attn_decode.py:496 (attn_decode_forward, fp16 K/V) and
+ *      src/lemoq/kernels/attn_decode.py:627 (attn_decode_forward_int8: int8 codes
+ *      with per-token fp16 scales folded into the scores / weights).
+ * q: (H, D) fp16; k, v: head h at base + h*kv_head_stride elements, (S, D) each;
+ * ks, vs: (H, S) fp16; out: (H, D) fp16; filled: device int32 scalar, clamped to
+ * [0, S] (a value outside sets *err_flag).  D in {64, 128}.  num_splits >= 1.
+ * workspace: lemoq_attn_workspace_bytes() bytes, zero-initialised once by the
+ * caller before first use (it holds arrival counters that every launch leaves at
+ * zero); launches sharing a workspace must not overlap on the GPU.
+ */
+LEMOQ_API size_t lemoq_attn_workspace_bytes(int heads, int D, int num_splits);
+LEMOQ_API int lemoq_attn_decode_fp16(const void* q, const void* k, const void* v, int64_t kv_head_stride,
+                           const int32_t* filled, void* out, int heads, int S, int D, int num_splits, float scale,
+                           void* workspace, int* err_flag, void* stream);
+LEMOQ_API int lemoq_attn_decode_int8(const void* q, const int8_t* kc, const void* ks, const int8_t* vc, const void* vs,
+                           int64_t kv_head_stride, const int32_t* filled, void* out, int heads, int S, int D,
+                           int num_splits, float scale, void* workspace, int* err_flag, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Router softmax + top-k: fp32 softmax over E logits, top_k rounds of arg-max
+ * (lowest index wins ties), optional renormalisation.
+ * ref: src/lemoq/kernels/_routing_triton.py:88 (routing_softmax_topk).
+ * logits: (T, E) fp16 or fp32, row stride in elements; top_w: (T, K) fp32;
+ * top_i: (T, K) int64.  E <= 1024.
+ */
+LEMOQ_API int lemoq_routing_softmax_topk(const void* logits, int logits_dtype, int64_t row_stride, int T, int E, int top_k,
+                               int norm_topk_prob, float* top_w, int64_t* top_i, void* stream);
+
+/* Router linear + softmax/top-k for one token: logits = fp16(h . Wr^T) with fp32
+ * accumulation, then as above; top_w is rounded to fp16.
+ * ref: src/lemoq/kernels/moe_static.py:262 (_route).
+ * h: (H,) fp16; router_w: (E, H) fp16; logits_out: (E,) fp16; top_w: (K,) fp16;
+ * top_i: (K,) int64.  E <= 64*32, H % 8 == 0.  workspace: 16 bytes, zeroed once.
+ */
+LEMOQ_API int lemoq_route(const void* h, const void* router_w, int E, int H, int top_k, int norm_topk_prob,
+                void* logits_out, void* top_w, int64_t* top_i, void* workspace, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Grouped expert GEMV, W8 weights dequantised in registers:
+ *   act[t,i,n] = silu(Wg[e,n,:].x_t) * (Wu[e,n,:].x_t), rounded to fp16;
+ *   out[t,n]   = fp16( sum_i top_w[t,i] * (Wd[e,n,:].act[t,i,:]) ),  e = ids[t,i].
+ * ref: src/lemoq/kernels/moe_grouped_quant.py:411 (grouped_moe_forward_quant) and
+ *      its kernels src/lemoq/kernels/_grouped_triton.py:249,335,197.
+ * x: (T, H) fp16; gu_codes: (E, 2F, H) int8 (gate rows [0,F), up rows [F,2F));
+ * gu_scale: (E, 2F, H/g) fp16; dn_codes: (E, H, F) int8; dn_scale: (E, H, F/g) fp16;
+ * ids: (T, K) int64; top_w: (T, K) fp16; act: (T, K, F) fp16 workspace (also an
+ * output); out: (T, H) fp16.  H, F multiples of 128 and <= 2048 / 8192; K <= 16.
+ * An expert id outside [0, E) is clamped and sets *err_flag.
+ */
+LEMOQ_API int lemoq_moe_grouped_w8(const void* x, const int8_t* gu_codes, const void* gu_scale, const int8_t* dn_codes,
+                         const void* dn_scale, const int64_t* ids, const void* top_w, int T, int K, int E, int H,
+                         int F, int group_size, void* act, void* out, int* err_flag, void* stream);
+
+/* Same contract on unquantised fp16 expert weights.
+ * ref: src/lemoq/kernels/moe_grouped.py:315 (grouped_moe_forward) and
+ *      src/lemoq/kernels/_grouped_triton.py:55,139.
+ */
+LEMOQ_API int lemoq_moe_grouped_fp16(const void* x, const void* gate_up, const void* down, const int64_t* ids,
+                           const void* top_w, int T, int K, int E, int H, int F, void* act, void* out,
+                           int* err_flag, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Whole decode step (one token, all layers, lm_head) as a fixed chain of fused
+ * kernels; the host captures one lemoq_step_run() call into a CUDA graph.
+ * ref: the forward captured by benchmarks/cudagraph.py:713 (StaticCacheDecodeSession
+ *      .capture) with every FUSION_DEFAULTS switch on
+ *      (src/lemoq/kernels/fusion_switches.py:50), i.e. per layer
+ *      src/lemoq/kernels/attn_decode.py:836 (_decode_forward_impl) followed by
+ *      src/lemoq/kernels/moe_grouped_quant.py:562 (static_moe_forward_grouped_quant).
+ */
+typedef struct lemoq_layer_desc {
+    const void* ln1;        /* (hidden) fp16 input_layernorm weight            */
+    const void* ln2;        /* (hidden) fp16 post_attention_layernorm weight   */
+    const void* q_norm;     /* (heads*head_dim) fp16                           */
+    const void* k_norm;     /* (heads*head_dim) fp16                           */
+    const int8_t* qkv_codes;/* (3*heads*head_dim, hidden) int8, rows [q;k;v]   */
+    const void* qkv_scale;  /* (3*heads*head_dim, hidden/g) fp16               */
+    const int8_t* o_codes;  /* (hidden, heads*head_dim) int8                   */
+    const void* o_scale;    /* (hidden, heads*head_dim/g) fp16                 */
+    const void* router;     /* (experts, hidden) fp16                          */
+    const int8_t* gu_codes; /* (experts, 2*ffn, hidden) int8                   */
+    const void* gu_scale;   /* (experts, 2*ffn, hidden/g) fp16                 */
+    const int8_t* dn_codes; /* (experts, hidden, ffn) int8                     */
+    const void* dn_scale;   /* (experts, hidden, ffn/g) fp16                   */
+    void* keys;             /* (heads, max_len, head_dim) fp16 static cache    */
+    void* values;           /* (heads, max_len, head_dim) fp16 static cache    */
+    int8_t* kc;             /* (heads, max_len, head_dim) int8 mirror (kv_int8)*/
+    void* ks;               /* (heads, max_len) fp16                           */
+    int8_t* vc;
+    void* vs;
+} lemoq_layer_desc;
+
+typedef struct lemoq_step_desc {
+    int layers, hidden, heads, head_dim, experts, top_k, ffn, vocab, group_size, max_len;
+    float eps;
+    int norm_topk_prob;
+    int kv_int8;            /* 1: attention reads the int8 mirror; 0: the fp16 cache       */
+    int attn_splits;        /* 0 = choose from the SM count                                 */
+    int use_pdl;            /* 1: programmatic dependent launch between the step's kernels  */
+    const void* embed;      /* (vocab, hidden) fp16                                         */
+    const void* final_norm; /* (hidden) fp16                                                */
+    const int8_t* lm_head_codes; /* (vocab, hidden) int8                                    */
+    const void* lm_head_scale;   /* (vocab, hidden/g) fp16                                  */
+    const void* rope_cos;   /* (max_len, head_dim) fp16                                     */
+    const void* rope_sin;
+    const int64_t* token;          /* device scalar: id of the token being decoded          */
+    const int64_t* cache_position; /* device scalar: its cache slot                         */
+    const int32_t* filled_len;     /* device scalar: cache_position + 1                     */
+    void* logits;           /* (vocab) fp16 output                                          */
+    void* workspace;        /* lemoq_step_workspace_bytes() bytes, zeroed once by the caller */
+    size_t workspace_bytes;
+} lemoq_step_desc;
+
+typedef struct lemoq_step lemoq_step; /* host-side plan, owns no device memory */
+
+LEMOQ_API size_t lemoq_step_workspace_bytes(const lemoq_step_desc* desc);
+LEMOQ_API int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_desc* layers, lemoq_step** out);
+LEMOQ_API void lemoq_step_destroy(lemoq_step* step);
+/* Enqueue one decode step.  Returns the number of kernels launched through
+ * *launches when it is not NULL. */
+LEMOQ_API int lemoq_step_run(lemoq_step* step, void* stream, int* launches);
+/* Device int32 inside the workspace: 0, or a bit mask of LEMOQ_FLAG_* set by a
+ * kernel that had to clamp a position, a length or an expert id. */
+LEMOQ_API int* lemoq_step_error_flag(lemoq_step* step);
+/* Device pointers to per-layer routing results of the last step (for parity
+ * checks): top_i (layers, top_k) int64 and router logits (layers, experts) fp16. */
+LEMOQ_API const int64_t* lemoq_step_topk_ids(lemoq_step* step);
+LEMOQ_API const void* lemoq_step_router_logits(lemoq_step* step);
+
+#define LEMOQ_FLAG_BAD_POSITION 1
+#define LEMOQ_FLAG_BAD_LENGTH 2
+#define LEMOQ_FLAG_BAD_EXPERT 4
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEMOQ_B200_H */

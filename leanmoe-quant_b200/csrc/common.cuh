@@ -1,0 +1,150 @@
+// Shared device helpers for the lemoq_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lemoq_b200.h"
+
+namespace lemoq {
+
+constexpr int kWarp = 32;
+
+// ---- error plumbing (host) -------------------------------------------------
+int set_error(int code, const char* fmt, ...);
+int check_launch(const char* what);
+
+#define LEMOQ_REQUIRE(cond, code, ...)                 \
+    do {                                               \
+        if (!(cond)) return ::lemoq::set_error(code, __VA_ARGS__); \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start before its predecessor finishes; pdl_wait() blocks until the
+// predecessor grid has completed and its writes are visible.  pdl_trigger()
+// lets the successor start its own prologue.  Both are no-ops for a normal
+// launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- loads -------------------------------------------------------------------
+// Streaming 128-bit load of read-once weight bytes: bypass L1 allocation.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// Coherent 128-bit load of data another kernel (or another block) just wrote.
+__device__ __forceinline__ uint4 ld_cg16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// ---- reductions -----------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the whole block; every thread gets the result.  `red` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    const float r = red[32];
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarp ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    const float r = red[32];
+    __syncthreads();
+    return r;
+}
+
+// ---- int8 / fp16 unpacking -----------------------------------------------------
+// Dot product of 16 int8 codes (one 128-bit word) with 16 fp32 activations.
+__device__ __forceinline__ float dot16_s8(const uint4& w, const float* x) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        a = fmaf(static_cast<float>(static_cast<int8_t>(u[i] & 0xffu)), x[4 * i + 0], a);
+        a = fmaf(static_cast<float>(static_cast<int8_t>((u[i] >> 8) & 0xffu)), x[4 * i + 1], a);
+        a = fmaf(static_cast<float>(static_cast<int8_t>((u[i] >> 16) & 0xffu)), x[4 * i + 2], a);
+        a = fmaf(static_cast<float>(static_cast<int8_t>(u[i] >> 24)), x[4 * i + 3], a);
+    }
+    return a;
+}
+// acc[j] += s * code[j] for 16 int8 codes.
+__device__ __forceinline__ void axpy16_s8(const uint4& w, float s, float* acc) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        acc[4 * i + 0] = fmaf(s, static_cast<float>(static_cast<int8_t>(u[i] & 0xffu)), acc[4 * i + 0]);
+        acc[4 * i + 1] = fmaf(s, static_cast<float>(static_cast<int8_t>((u[i] >> 8) & 0xffu)), acc[4 * i + 1]);
+        acc[4 * i + 2] = fmaf(s, static_cast<float>(static_cast<int8_t>((u[i] >> 16) & 0xffu)), acc[4 * i + 2]);
+        acc[4 * i + 3] = fmaf(s, static_cast<float>(static_cast<int8_t>(u[i] >> 24)), acc[4 * i + 3]);
+    }
+}
+// 8 fp16 values (one 128-bit word) to fp32.
+__device__ __forceinline__ void unpack8_h(const uint4& w, float* out) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&u[i]);
+        const float2 f = __half22float2(h);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ float dot8_h(const uint4& w, const float* x) {
+    float f[8];
+    unpack8_h(w, f);
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a = fmaf(f[i], x[i], a);
+    return a;
+}
+
+// HF RMSNorm rounding chain for one element: fp16(x * rstd) then an fp16 multiply
+// by the weight; returned widened to fp32.
+__device__ __forceinline__ float norm_elem(__half x, float rstd, __half w) {
+    const __half n = __float2half_rn(__half2float(x) * rstd);
+    return __half2float(__hmul(n, w));
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+}  // namespace lemoq
