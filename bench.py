@@ -1,0 +1,411 @@
+"""Benchmark of the hot path: batch-1 greedy decode of the canonical OLMoE cell.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--ctx 1024] [--impl reference]
+
+Workload (BASELINE config 2): full OLMoE-1B-7B architecture (16 layers, hidden 2048, 64 experts top-8,
+expert FFN 1024, vocab 50304), seeded random-init fp16 weights, canonical quantisation W8A16 g128 +
+lm_head W8 + per-token INT8 KV, all-ones prompt of ``ctx`` tokens prefilled, then greedy decode.
+A "step" is one decoded token = one replay of the captured step graph.
+
+Printed JSON line (rank 0):
+  value   tokens/s with the step inputs already on the device: K graph replays at advancing
+          positions, device-timed with CUDA events, no host read-back inside the region.
+  e2e     tokens/s through the public session API with host buffers: per step the token id and
+          position are copied from pinned host memory, the graph runs, the next token id is read
+          back (this is the reference's replay_timed_step loop).
+  roofline  the dominant kernel (expert gate/up GEMV) timed alone with CUDA events on L2-flushed
+          launches, algorithmic bytes / time against the measured HBM copy bandwidth; plus the
+          whole-step byte-floor fraction.
+  cpu_baseline  the CPU oracle (a port of the reference's torch CPU path) on a bounded sample.
+
+``--impl reference`` times only that CPU implementation (all host threads) on the same configuration.
+With ``--gpus N`` (under torchrun) batch-1 decode does not shard: every rank runs an independent
+replica ("replicas only"), the reported value is the sum over ranks with the max-over-ranks time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "leanmoe-quant_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "decode_tokens_per_s_batch1"
+UNIT = "tok/s"
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, earlier measurement on this pool)"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's torch CPU path on synthetic quantised weights
+# ----------------------------------------------------------------------------------------------
+def synthetic_oracle_weights(spec, seed: int = 0):
+    """Quantised weights drawn directly (int8 codes uniform, fp16 scales |N(0,1)|*0.01 scaled down):
+    the values do not change the work a step does, and drawing codes avoids minutes of CPU RTN."""
+    import torch
+
+    from oracle import lemoq_oracle as ops
+    from oracle import olmoe_decode_oracle as glue
+
+    g = torch.Generator().manual_seed(seed)
+
+    def codes(*shape):
+        return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8)
+
+    def scales(*shape):
+        return (torch.rand(shape, generator=g) * 2.0e-4 + 1.0e-4).half()
+
+    h, a, e, f, grp = spec.hidden, spec.attn_dim, spec.experts, spec.ffn, spec.group_size
+    ones = torch.ones(h, dtype=torch.float16)
+    layers = []
+    for _ in range(spec.layers):
+        ex = ops.QuantExperts(codes(e, 2 * f, h), scales(e, 2 * f, h // grp), codes(e, h, f), scales(e, h, f // grp), grp)
+        layers.append(glue.LayerWeights(ln1=ones, ln2=ones, q_norm=torch.ones(a, dtype=torch.float16),
+                                        k_norm=torch.ones(a, dtype=torch.float16),
+                                        router=(torch.randn(e, h, generator=g) * 0.02).half(),
+                                        qkv_codes=codes(3 * a, h), qkv_scale=scales(3 * a, h // grp),
+                                        o_codes=codes(h, a), o_scale=scales(h, a // grp), experts=ex))
+    return glue.ModelWeights(spec=spec, embed=(torch.randn(spec.vocab, h, generator=g) * 0.02).half(), layers=layers,
+                             final_norm=ones, lm_head_codes=codes(spec.vocab, h), lm_head_scale=scales(spec.vocab, h // grp),
+                             quantized=True)
+
+
+def time_oracle_steps(wq, st, first_token: int, ctx: int, steps: int, warmup: int):
+    """Greedy decode on the CPU oracle; returns the list of per-step seconds (timed steps only)."""
+    import torch
+
+    from oracle import olmoe_decode_oracle as glue
+
+    tok, times = int(first_token), []
+    for s in range(warmup + steps):
+        t0 = time.perf_counter()
+        lg = glue.decode_step(wq, st, tok, ctx + s, kv_int8=True)
+        tok = int(torch.argmax(lg.float()))
+        if s >= warmup:
+            times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args) -> int:
+    """The reference arm: the CPU implementation of the decode step on the host cores."""
+    import torch
+
+    from oracle import olmoe_decode_oracle as glue
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    spec = glue.OlmoeSpec()
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    wq = synthetic_oracle_weights(spec)
+    st = glue.new_state(spec, args.ctx + steps + warmup)
+    g = torch.Generator().manual_seed(1)
+    for i in range(spec.layers):
+        st.keys[i][:, :, : args.ctx] = torch.randn(1, spec.heads, args.ctx, spec.head_dim, generator=g).half()
+        st.values[i][:, :, : args.ctx] = torch.randn(1, spec.heads, args.ctx, spec.head_dim, generator=g).half()
+    glue.build_int8_mirror(st)
+    times = time_oracle_steps(wq, st, 1, args.ctx, steps, warmup)
+    ms = 1000.0 * sum(times) / len(times)
+    value = 1000.0 / ms
+    sample = "%d decode steps of the 16-layer canonical model at ctx %d (synthetic int8 codes, random fp16 KV)" % (steps, args.ctx)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, ctx %d" % args.ctx,
+                   "ctx": args.ctx, "layers": spec.layers},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def time_dominant_kernel(model, peaks, iters: int = 20) -> dict:
+    """Expert gate/up GEMV (the kernel with the largest byte share of a step) timed alone: one launch
+    per event pair on the current stream, a 256 MB L2 flush before every launch."""
+    import torch
+
+    from lemoq import _cabi
+
+    cfg = model.config
+    ex = model.model.layers[0].mlp._static_experts
+    dev = ex.packed_gate_up.device
+    k, h, f, e = cfg.num_experts_per_tok, cfg.hidden_size, cfg.intermediate_size, cfg.num_experts
+    x = torch.randn(h, device=dev).half()
+    act = torch.empty((k, f), dtype=torch.float16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    stream = _cabi.current_stream(dev)
+    times = []
+    for i in range(iters + 3):
+        ids = (torch.randperm(e, device=dev)[:k]).to(torch.int64)
+        layer = model.model.layers[i % cfg.num_hidden_layers].mlp._static_experts
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        _cabi.call("lemoq_moe_gate_up_w8", _cabi.ptr(x), _cabi.ptr(layer.packed_gate_up), _cabi.ptr(layer.scale_gate_up),
+                   _cabi.ptr(ids), 1, k, e, h, f, int(layer.group_size), _cabi.ptr(act), None, stream)
+        end.record()
+        end.synchronize()
+        if i >= 3:
+            times.append(start.elapsed_time(end) * 1e-3)
+    # event-pair floor (empty region) so that launch latency is not booked as bandwidth
+    floor = []
+    for _ in range(10):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        end.record()
+        end.synchronize()
+        floor.append(start.elapsed_time(end) * 1e-3)
+    nbytes = k * (2 * f * h + 2 * f * (h // int(ex.group_size)) * 2) + h * 2 + k * f * 2
+    t = statistics.median(times)
+    achieved = nbytes / t / 1e9
+    return {"bound": "hbm", "kernel": "moe_gate_up_kernel<4,true> (expert gate/up W8 GEMV + SwiGLU)", "achieved": achieved,
+            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+            "bytes_per_launch": nbytes, "us_per_launch": t * 1e6, "event_floor_us": statistics.median(floor) * 1e6,
+            "peak_source": peaks["source"], "timing": "CUDA events, isolated launches, 256 MB L2 flush before each"}
+
+
+def run_gpu(args) -> int:
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    device = "cuda:%d" % local_rank
+
+    from benchmarks.bytes import CANONICAL_QUANT, ModelSpec, byte_budget
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+    from benchmarks.runner import build_model, install_replacements
+    from lemoq import _cabi
+
+    _cabi.lib()  # the CUDA library must be there: no fallback
+    peaks = measured_peaks()
+    steps, warmup, ctx = max(1, args.steps), max(3, args.warmup), args.ctx
+    horizon = steps + warmup + 2
+    model = build_model(seed=0, device=device, layers=args.layers)
+    install_replacements(model, attn="kernel", moe="grouped",
+                         quant_cfg={"bit_width": "w8a16", "dequant": "fused", "group_size": 128}, rmsnorm="fused",
+                         ctx=ctx, max_new_tokens=horizon, device=device)
+    prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
+    session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine=args.engine)
+    session.capture(warmup=3)
+    launches_per_step = int(session.capture_info.get("kernels_per_step") or 0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    # ---------------- value: device-resident inputs, K replays at advancing positions ----------------
+    session.reset()
+    for _ in range(warmup):
+        session.replay(synchronize=True)
+    start_pos = session.position
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(session.stream):
+        ev0.record(session.stream)
+        for i in range(steps):
+            session.position = start_pos + i
+            session.replay(synchronize=False)
+        ev1.record(session.stream)
+    session.stream.synchronize()
+    barrier()
+    dev_ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+    # ---------------- e2e: host buffers in, token id out, every step ----------------
+    session.reset()
+    for _ in range(warmup):
+        session.replay(synchronize=True)
+    pinned_in = torch.zeros(4, dtype=torch.int64).pin_memory()
+    pinned_out = torch.zeros(1, dtype=torch.int64).pin_memory()
+    dev_in = torch.zeros(4, dtype=torch.int64, device=device)
+    b = session.buffers
+    tok, pos = session.current_token_id, session.position
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    with torch.cuda.stream(session.stream):
+        e0.record(session.stream)
+        for i in range(steps):
+            pinned_in[0], pinned_in[1], pinned_in[2] = tok, pos + i, pos + i + 1
+            dev_in.copy_(pinned_in, non_blocking=True)  # H2D of this step's inputs
+            b.token.copy_(dev_in[0:1].view(1, 1))
+            b.cache_position.copy_(dev_in[1:2])
+            b.position_ids.copy_(dev_in[1:2].view(1, 1))
+            b.filled_len.copy_(dev_in[2:3])
+            session.graph.replay()
+            pinned_out.copy_(session.logits.reshape(-1).argmax().reshape(1), non_blocking=True)  # D2H of the result
+            session.stream.synchronize()
+            tok = int(pinned_out[0])
+        e1.record(session.stream)
+    session.stream.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1000.0 / steps
+    barrier()
+    clocks = sampler.stop()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / steps, wall_ms))
+
+    spec = ModelSpec.from_config(model.config)
+    budget = byte_budget(spec, ctx + warmup + steps // 2 + 1, CANONICAL_QUANT, kv_int8=True)
+    floor_ms = budget["T"] / (peaks["hbm_gbs"] * 1e9) * 1e3
+    result = {
+        "metric": METRIC, "value": world * 1000.0 / dev_ms, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, "
+                               "ctx %d, one CUDA graph per step (BASELINE config 2)" % ctx,
+                   "ctx": ctx, "layers": model.config.num_hidden_layers, "engine": session.capture_info.get("engine"),
+                   "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0",
+                   "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (budget["T"] / 1e9),
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "ms_per_token": dev_ms, "bytes_per_step": budget["T"], "byte_floor_ms": floor_ms,
+        "floor_fraction": floor_ms / dev_ms, "floor_fraction_e2e": floor_ms / e2e_ms,
+        "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": 32,
+                "d2h_bytes_per_step": 8},
+        "gpu_launches": launches_per_step * steps * 2, "kernels_per_step": launches_per_step, "clocks": clocks,
+    }
+    if rank == 0:
+        result["roofline"] = time_dominant_kernel(model, peaks)
+        result["roofline"]["step_floor_fraction"] = floor_ms / dev_ms
+        if not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_baseline_from_session(session, model, spec, ctx, warmup)
+    session.close()
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def cpu_baseline_from_session(session, model, spec_bytes, ctx: int, warmup: int) -> dict:
+    """The oracle on this box's host cores, same weights (copied from the GPU) and prefilled cache."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from gpu_util import oracle_state_from_session, oracle_weights_from_model
+    from oracle import olmoe_decode_oracle as glue
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    spec = glue.OlmoeSpec(layers=model.config.num_hidden_layers)
+    session.reset()
+    wq = oracle_weights_from_model(model, spec)
+    st = oracle_state_from_session(session, spec)
+    n = 6
+    times = time_oracle_steps(wq, st, session.seed_token_id, ctx, n, 1)
+    ms = 1000.0 * sum(times) / len(times)
+    return {"value": 1000.0 / ms, "unit": UNIT, "ms_per_step": ms, "cores": cores, "kind": "port",
+            "sample": "%d greedy decode steps of the same model and prefilled cache on the CPU oracle (1 warm-up)" % n}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "step", "ops"])
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -175,6 +175,17 @@ LEMOQ_API int lemoq_moe_grouped_w8(const void* x, const int8_t* gu_codes, const 
                          const void* dn_scale, const int64_t* ids, const void* top_w, int T, int K, int E, int H,
                          int F, int group_size, void* act, void* out, int* err_flag, void* stream);
 
+/* The two launches of lemoq_moe_grouped_w8 on their own (same arguments; gate_up reads x and
+ * writes act, down reads act and writes out).
+ * ref: src/lemoq/kernels/_grouped_triton.py:249 (_gate_up_act_kernel_q) and
+ *      src/lemoq/kernels/_grouped_triton.py:335 (_down_sum_kernel_q).
+ */
+LEMOQ_API int lemoq_moe_gate_up_w8(const void* x, const int8_t* gu_codes, const void* gu_scale, const int64_t* ids, int T,
+                         int K, int E, int H, int F, int group_size, void* act, int* err_flag, void* stream);
+LEMOQ_API int lemoq_moe_down_w8(const void* act, const int8_t* dn_codes, const void* dn_scale, const int64_t* ids,
+                      const void* top_w, int T, int K, int E, int H, int F, int group_size, void* out, int* err_flag,
+                      void* stream);
+
 /* Same contract on unquantised fp16 expert weights.
  * ref: src/lemoq/kernels/moe_grouped.py:315 (grouped_moe_forward) and
  *      src/lemoq/kernels/_grouped_triton.py:55,139.

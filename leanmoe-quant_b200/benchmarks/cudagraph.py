@@ -239,6 +239,7 @@ class StaticCacheDecodeSession:
         self._attn_splits = int(attn_splits)
         self._step = None  # native step plan (built lazily, after the first prefill)
         self.engine = None
+        self.after_prefill = None  # optional callable(session): runs at the end of every prefill
         self.prefill()
 
     # ------------------------------------------------------------------ prefill
@@ -256,8 +257,9 @@ class StaticCacheDecodeSession:
                                 cache_position=positions, position_ids=positions.unsqueeze(0))
         self.current_token_id = int(output.logits[:, -1:, :].argmax(dim=-1).item())
         self.position = self.config.ctx
-        if self._step is not None:
-            self._requantize_mirror()
+        if self.after_prefill is not None:
+            self.after_prefill(self)
+        self._requantize_mirror()
         if self._cuda_available:
             torch.cuda.synchronize()
         return output
@@ -393,15 +395,24 @@ class StaticCacheDecodeSession:
         self.capture_info["pdl"] = bool(self._use_pdl)
 
     def _requantize_mirror(self) -> None:
-        """After a (re)prefill: rebuild every layer's int8 mirror in place from the fp16 cache."""
-        if self._step is None or not self._step["kv_int8"]:
+        """After a (re)prefill: rebuild, in place, every int8 mirror that was built from this
+        session's cache (both engines keep it on the attention module), so slots written by earlier
+        decode steps cannot leak into the next sequence."""
+        if not self._cuda_available:
             return
         from lemoq import _cabi
 
-        stream = _cabi.current_stream(self.device)
+        stream = None
         for i, layer in enumerate(self.model.model.layers):
-            bufs = layer.self_attn._lemoq_kv_int8_bufs
+            attn = getattr(layer, "self_attn", None)
+            bufs = getattr(attn, "_lemoq_kv_int8_bufs", None)
+            ref = getattr(attn, "_lemoq_kv_int8_src_cache_ref", None)
             cl = self.cache.layers[i]
+            if bufs is None or ref is None or ref() is not self.cache or not cl.is_initialized:
+                continue
+            if tuple(bufs["kc"].shape) != tuple(cl.keys.shape):
+                continue
+            stream = _cabi.current_stream(self.device) if stream is None else stream
             _, h, s, d = (int(v) for v in cl.keys.shape)
             _cabi.call("lemoq_kv_int8_bulk_quantize", _cabi.ptr(cl.keys), _cabi.ptr(cl.values), _cabi.ptr(bufs["kc"]),
                        _cabi.ptr(bufs["ks"]), _cabi.ptr(bufs["vc"]), _cabi.ptr(bufs["vs"]), h, s, d, -1, stream)

@@ -276,3 +276,33 @@ extern "C" int lemoq_moe_grouped_fp16(const void* x, const void* gate_up, const 
     if (int rc = launch_moe_gate_up(p, false, lc)) return rc;
     return launch_moe_down(p, false, lc);
 }
+
+extern "C" int lemoq_moe_gate_up_w8(const void* x, const int8_t* gu_codes, const void* gu_scale, const int64_t* ids, int T,
+                                    int K, int E, int H, int F, int group_size, void* act, int* err_flag, void* stream) {
+    MoeParams p;
+    // top_w / out are unused by this launch; pass act for both so that the common checks hold
+    if (int rc = moe_common(p, x, ids, act, T, K, E, H, F, act, act, err_flag)) return rc;
+    LEMOQ_REQUIRE(gu_codes && gu_scale, LEMOQ_ERR_INVALID, "moe_gate_up_w8: null weight pointer");
+    LEMOQ_REQUIRE(group_size > 0 && group_size % 16 == 0 && H % group_size == 0, LEMOQ_ERR_INVALID,
+                  "moe_gate_up_w8: hidden=%d / group_size=%d", H, group_size);
+    if (T == 0) return LEMOQ_OK;
+    p.gate_up = gu_codes;
+    p.gu_scale = reinterpret_cast<const __half*>(gu_scale);
+    p.group_size = group_size;
+    return launch_moe_gate_up(p, true, cfg_of(stream));
+}
+
+extern "C" int lemoq_moe_down_w8(const void* act, const int8_t* dn_codes, const void* dn_scale, const int64_t* ids,
+                                 const void* top_w, int T, int K, int E, int H, int F, int group_size, void* out,
+                                 int* err_flag, void* stream) {
+    MoeParams p;
+    if (int rc = moe_common(p, act, ids, top_w, T, K, E, H, F, const_cast<void*>(act), out, err_flag)) return rc;
+    LEMOQ_REQUIRE(dn_codes && dn_scale, LEMOQ_ERR_INVALID, "moe_down_w8: null weight pointer");
+    LEMOQ_REQUIRE(group_size > 0 && group_size % 16 == 0 && F % group_size == 0, LEMOQ_ERR_INVALID,
+                  "moe_down_w8: ffn=%d / group_size=%d", F, group_size);
+    if (T == 0) return LEMOQ_OK;
+    p.down = dn_codes;
+    p.dn_scale = reinterpret_cast<const __half*>(dn_scale);
+    p.group_size = group_size;
+    return launch_moe_down(p, true, cfg_of(stream));
+}

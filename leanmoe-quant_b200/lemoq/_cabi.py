@@ -68,6 +68,10 @@ _SIGNATURES = {
                             c_void_p]),
     "lemoq_moe_grouped_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lemoq_moe_gate_up_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p]),
+    "lemoq_moe_down_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, c_void_p, c_void_p, c_void_p]),
     "lemoq_moe_grouped_fp16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "lemoq_step_workspace_bytes": (c_size_t, [POINTER(StepDesc)]),
