@@ -49,6 +49,14 @@ extern "C" {
 LEMOQ_API const char* lemoq_version(void);
 LEMOQ_API const char* lemoq_last_error(void);
 
+/* Kernel tuning knobs for benchmarking (process-wide, not thread-safe; defaults are the measured
+ * best).  key 0: int8 dot-product mode of the streaming kernels (0 = fp32 magic-number, 1 = exact
+ * fp16 codes widened to fp32, 2 = exact fp16 codes with mixed-precision FMA); key 1: warps per block
+ * of the streaming kernels (1..16).  No counterpart in the reference, whose tile configs are module
+ * dicts (src/lemoq/kernels/moe_grouped.py:78, src/lemoq/kernels/_dequant_triton.py:83).
+ */
+LEMOQ_API int lemoq_set_tuning(int key, int value);
+
 /* ---------------------------------------------------------------------------
  * Weight quantisation: per-row, per-group symmetric RTN to int8.
  * ref: src/lemoq/quant/rtn.py:38 (quantize_rtn, symmetric 8-bit branch),
@@ -261,10 +269,14 @@ LEMOQ_API int* lemoq_step_error_flag(lemoq_step* step);
  * checks): top_i (layers, top_k) int64 and router logits (layers, experts) fp16. */
 LEMOQ_API const int64_t* lemoq_step_topk_ids(lemoq_step* step);
 LEMOQ_API const void* lemoq_step_router_logits(lemoq_step* step);
+/* Device pointer to 6*layers + 2 global-timer stamps (ns) taken by the whole-step kernel at its start and
+ * after each phase barrier of the last step; NULL when the step runs as chained kernels. */
+LEMOQ_API const unsigned long long* lemoq_step_phase_stamps(lemoq_step* step);
 
 #define LEMOQ_FLAG_BAD_POSITION 1
 #define LEMOQ_FLAG_BAD_LENGTH 2
 #define LEMOQ_FLAG_BAD_EXPERT 4
+#define LEMOQ_FLAG_WAIT_TIMEOUT 8 /* a bounded wait on an async copy gave up */
 
 #ifdef __cplusplus
 }

@@ -52,9 +52,10 @@ class Timer:
         """Median microseconds of ``fn()`` over L2-flushed single calls."""
         out = []
         for i in range(self.iters + 3):
-            if setup is not None:
+            if setup is not None and not (getattr(self, "warm", False) and i > 0):
                 setup(i)
-            self.flush.zero_()
+            if not getattr(self, "warm", False):
+                self.flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -193,13 +194,25 @@ def main() -> int:
     ap.add_argument("--tokens", default="1,4,16")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--bandwidth-gbs", type=float, default=None)
+    ap.add_argument("--dot-mode", type=int, default=None, help="lemoq_set_tuning key 0 (0 magic fp32, 1 exact cvt, 2 exact mixed)")
+    ap.add_argument("--debug", type=int, default=None, help="lemoq_set_tuning key 2 (timing experiments, wrong results)")
+    ap.add_argument("--warm", action="store_true", help="no L2 flush between calls (data served from L2 when it fits)")
+    ap.add_argument("--warps", type=int, default=None, help="lemoq_set_tuning key 1: warps per block of the streaming kernels")
     args = ap.parse_args()
     peak = args.bandwidth_gbs
     if peak is None:
         path = os.path.join(os.path.dirname(_PKG), "MEASURED_PEAKS.json")
         peak = float(json.load(open(path))["hbm_gbs"]) if os.path.exists(path) else 6650.0
     _cabi.lib()
+    if args.dot_mode is not None:
+        _cabi.call("lemoq_set_tuning", 0, args.dot_mode)
+    if args.warps is not None:
+        _cabi.call("lemoq_set_tuning", 1, args.warps)
+    if args.debug is not None:
+        _cabi.call("lemoq_set_tuning", 2, args.debug)
+    print(json.dumps({"tuning": {"dot_mode": args.dot_mode, "warps": args.warps}}), flush=True)
     timer = Timer(args.iters)
+    timer.warm = args.warm
     if args.subject in ("moe", "all"):
         bench_moe(timer, [int(t) for t in args.tokens.split(",")], peak)
     if args.subject in ("dense", "all"):

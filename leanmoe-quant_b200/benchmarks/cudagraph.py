@@ -457,6 +457,24 @@ class StaticCacheDecodeSession:
         self.torch.cuda.synchronize()
         return self._step["workspace"][off: off + 8 * n].view(self.torch.int64).reshape(cfg.num_hidden_layers, -1).clone()
 
+    def step_phase_times_us(self) -> Any:
+        """Per-phase durations (us) of the last whole-step kernel: a (layers, 6) tensor for the phases
+        q.k.v / attention / o_proj / router / gate_up / down plus the lm_head time; None when the step
+        runs as chained kernels."""
+        if self._step is None:
+            return None
+        from lemoq import _cabi
+
+        addr = _cabi.lib().lemoq_step_phase_stamps(self._step["handle"])
+        if not addr:
+            return None
+        layers = self.model.config.num_hidden_layers
+        off = int(addr) - int(self._step["workspace"].data_ptr())
+        self.torch.cuda.synchronize()
+        st = self._step["workspace"][off: off + 8 * (6 * layers + 2)].view(self.torch.int64).cpu().double()
+        d = (st[1:] - st[:-1]) / 1000.0
+        return {"phases": d[: 6 * layers].reshape(layers, 6), "lm_head": float(d[6 * layers]), "total": float((st[-1] - st[0]) / 1000.0)}
+
     # ------------------------------------------------------------------ decode
     def decode_eager(self) -> Any:
         if self.current_token_id is None:

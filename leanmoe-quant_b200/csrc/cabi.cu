@@ -28,6 +28,7 @@ using namespace lemoq;
 
 extern "C" const char* lemoq_version(void) { return "lemoq_b200 0.1 (sm_100a)"; }
 extern "C" const char* lemoq_last_error(void) { return g_err; }
+extern "C" int lemoq_set_tuning(int key, int value) { return set_stream_tuning(key, value); }
 
 extern "C" int lemoq_rtn_quantize_w8(const void* w, int w_dtype, int64_t rows, int in_features, int group_size,
                                      int8_t* codes, void* scale, void* stream) {

@@ -89,6 +89,7 @@ static int launch_gemv_nch(const GemvParams& p, int M, bool norm, bool resid, bo
 }
 
 int launch_gemv_w8(const GemvParams& p, int M, bool norm, bool resid, bool out_f32, const LaunchCfg& lc) {
+    if (!out_f32 && stream_gemv_eligible(p, M)) return launch_stream_gemv_w8(p, norm, resid, lc);
     const int nch = (p.K + 511) / 512;
     switch (nch) {
         case 1: return launch_gemv_nch<1, 2>(p, M, norm, resid, out_f32, lc);

@@ -54,8 +54,13 @@ struct GemvParams {
     const __half* resid = nullptr;   // (M, N) fp16 for the residual epilogue
     int64_t resid_stride = 0;
     const int64_t* resid_token = nullptr;
+    int* err_flag = nullptr;
 };
 int launch_gemv_w8(const GemvParams& p, int M, bool norm, bool resid, bool out_f32, const LaunchCfg& lc);
+// persistent bulk-copy streaming variants (stream_gemv.cu); the *_eligible predicates state their shape rules
+bool stream_gemv_eligible(const GemvParams& p, int M);
+int set_stream_tuning(int key, int value);
+int launch_stream_gemv_w8(const GemvParams& p, bool norm, bool resid, const LaunchCfg& lc);
 
 // ---- router ----------------------------------------------------------------------
 struct RouteParams {
@@ -88,9 +93,13 @@ struct MoeParams {
     __half* out = nullptr;           // (T, H)
     const __half* resid = nullptr;   // optional (T, H): out = fp16(acc) + resid
     int* err_flag = nullptr;
+    int debug = 0;                   // timing experiments (lemoq_set_tuning key 2)
 };
 int launch_moe_gate_up(const MoeParams& p, bool w8, const LaunchCfg& lc);
 int launch_moe_down(const MoeParams& p, bool w8, const LaunchCfg& lc);
+bool stream_moe_eligible(const MoeParams& p);
+int launch_stream_gate_up(const MoeParams& p, const LaunchCfg& lc);
+int launch_stream_down(const MoeParams& p, const LaunchCfg& lc);
 
 // ---- attention --------------------------------------------------------------------
 struct AttnParams {

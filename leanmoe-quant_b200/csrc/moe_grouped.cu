@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeParams p) {
 }
 
 int launch_moe_gate_up(const MoeParams& p, bool w8, const LaunchCfg& lc) {
+    if (w8 && stream_moe_eligible(p)) return launch_stream_gate_up(p, lc);
     const int warps = 8;
     dim3 grid((p.F + warps - 1) / warps, p.K, p.T), block(warps * 32);
     const int nch = (p.H + 511) / 512;
@@ -183,6 +184,7 @@ static int launch_down_nchf(const MoeParams& p, const LaunchCfg& lc) {
 }
 
 int launch_moe_down(const MoeParams& p, bool w8, const LaunchCfg& lc) {
+    if (w8 && stream_moe_eligible(p)) return launch_stream_down(p, lc);
     const int nchf = (p.F + 511) / 512;
 #define LEMOQ_DN_CASE(N) \
     case N:              \

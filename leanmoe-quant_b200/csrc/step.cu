@@ -14,6 +14,7 @@
 #include <new>
 
 #include "kernels.h"
+#include "step_mega.h"
 
 struct lemoq_step {
     lemoq_step_desc d;
@@ -33,6 +34,12 @@ struct lemoq_step {
     __half* top_w;          // (top_k)
     int64_t* top_i;         // (layers, top_k)
     float* attn_part;
+    // whole-step cooperative kernel
+    unsigned int* bar_counter;
+    unsigned int* bar_epoch;
+    lemoq::MegaLayer* mega_layers;  // device copy of the layer descriptors
+    int mega_grid;                  // 0 = chained kernels
+    unsigned long long* stamps;     // phase time stamps of the whole-step kernel
 };
 
 namespace lemoq {
@@ -83,6 +90,10 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(top_w, __half*, sizeof(__half) * d.top_k);
     LEMOQ_TAKE(top_i, int64_t*, sizeof(int64_t) * d.layers * d.top_k);
     LEMOQ_TAKE(attn_part, float*, sizeof(float) * d.heads * splits * (d.head_dim + 2));
+    LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
+    LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
+    LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * d.layers);
+    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2));
 #undef LEMOQ_TAKE
     return c.off;
 }
@@ -108,6 +119,11 @@ static int validate(const lemoq_step_desc& d) {
 }
 
 }  // namespace lemoq
+
+namespace lemoq {
+int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
+int g_step_use_mega = 0;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
+}
 
 using namespace lemoq;
 
@@ -143,6 +159,51 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
     for (int l = 0; l < desc->layers; ++l) s->layers[l] = layers[l];
     s->splits = splits;
     carve(*desc, splits, s);
+    s->mega_grid = 0;
+    if (g_step_use_mega && mega_eligible(*desc)) {
+        const int grid = mega_grid(*desc, splits);
+        if (grid > 0) {
+            // attention units are (head, split) blocks: at most one per resident block
+            int ms = grid / desc->heads;
+            if (ms < 1) ms = 1;
+            if (desc->attn_splits > 0 && desc->attn_splits < ms) ms = desc->attn_splits;
+            if (desc->heads * ms <= grid && ms <= splits) {
+                MegaLayer* host = new (std::nothrow) MegaLayer[desc->layers];
+                if (host) {
+                    for (int l = 0; l < desc->layers; ++l) {
+                        const lemoq_layer_desc& L = layers[l];
+                        MegaLayer& m = host[l];
+                        m.ln1 = reinterpret_cast<const __half*>(L.ln1);
+                        m.ln2 = reinterpret_cast<const __half*>(L.ln2);
+                        m.q_norm = reinterpret_cast<const __half*>(L.q_norm);
+                        m.k_norm = reinterpret_cast<const __half*>(L.k_norm);
+                        m.qkv_codes = L.qkv_codes;
+                        m.qkv_scale = reinterpret_cast<const __half*>(L.qkv_scale);
+                        m.o_codes = L.o_codes;
+                        m.o_scale = reinterpret_cast<const __half*>(L.o_scale);
+                        m.router = reinterpret_cast<const __half*>(L.router);
+                        m.gu_codes = L.gu_codes;
+                        m.gu_scale = reinterpret_cast<const __half*>(L.gu_scale);
+                        m.dn_codes = L.dn_codes;
+                        m.dn_scale = reinterpret_cast<const __half*>(L.dn_scale);
+                        m.keys = reinterpret_cast<__half*>(L.keys);
+                        m.values = reinterpret_cast<__half*>(L.values);
+                        m.kc = L.kc;
+                        m.ks = reinterpret_cast<__half*>(L.ks);
+                        m.vc = L.vc;
+                        m.vs = reinterpret_cast<__half*>(L.vs);
+                    }
+                    // set-up time only: the descriptors move to the device once (synchronous copy)
+                    const cudaError_t err = cudaMemcpy(s->mega_layers, host, sizeof(MegaLayer) * desc->layers, cudaMemcpyHostToDevice);
+                    delete[] host;
+                    if (err == cudaSuccess) {
+                        s->mega_grid = grid;
+                        s->splits = ms;
+                    }
+                }
+            }
+        }
+    }
     *out = s;
     return LEMOQ_OK;
 }
@@ -156,6 +217,7 @@ extern "C" void lemoq_step_destroy(lemoq_step* s) {
 extern "C" int* lemoq_step_error_flag(lemoq_step* s) { return s ? s->err_flag : nullptr; }
 extern "C" const int64_t* lemoq_step_topk_ids(lemoq_step* s) { return s ? s->top_i : nullptr; }
 extern "C" const void* lemoq_step_router_logits(lemoq_step* s) { return s ? s->router_logits : nullptr; }
+extern "C" const unsigned long long* lemoq_step_phase_stamps(lemoq_step* s) { return (s && s->mega_grid > 0) ? s->stamps : nullptr; }
 
 extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
     LEMOQ_REQUIRE(s, LEMOQ_ERR_INVALID, "step_run: null step");
@@ -167,6 +229,31 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
     lc.pdl = d.use_pdl != 0;
     lc.launch_count = &count;
     const float qk = (1.0f / sqrtf(static_cast<float>(d.head_dim))) * 1.4426950408889634f;
+
+    if (s->mega_grid > 0 && g_step_use_mega && g_step_skip_mask == 0) {
+        MegaParams p;
+        p.layers = d.layers; p.H = d.hidden; p.heads = d.heads; p.D = d.head_dim; p.E = d.experts; p.K = d.top_k;
+        p.F = d.ffn; p.V = d.vocab; p.group = d.group_size; p.S = d.max_len; p.splits = s->splits;
+        p.kv_int8 = d.kv_int8; p.norm_topk = d.norm_topk_prob; p.eps = d.eps; p.qk_scale_log2 = qk;
+        p.embed = reinterpret_cast<const __half*>(d.embed);
+        p.final_norm = reinterpret_cast<const __half*>(d.final_norm);
+        p.lm_scale = reinterpret_cast<const __half*>(d.lm_head_scale);
+        p.rope_cos = reinterpret_cast<const __half*>(d.rope_cos);
+        p.rope_sin = reinterpret_cast<const __half*>(d.rope_sin);
+        p.lm_codes = d.lm_head_codes;
+        p.token = d.token; p.cache_position = d.cache_position; p.filled = d.filled_len;
+        p.logits = reinterpret_cast<__half*>(d.logits);
+        p.L = s->mega_layers;
+        p.err_flag = s->err_flag; p.bar_counter = s->bar_counter; p.bar_epoch = s->bar_epoch;
+        p.attn_counters = s->attn_counters;
+        p.qkv = s->qkv; p.attn = s->attn; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
+        p.router_logits = s->router_logits; p.top_w = s->top_w; p.top_i = s->top_i; p.attn_part = s->attn_part;
+        p.barriers_per_launch = 6 * d.layers + 1;
+        p.stamps = s->stamps;
+        if (int rc = launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream))) return rc;
+        if (launches) *launches = 1;
+        return LEMOQ_OK;
+    }
 
     const __half* x_prev = reinterpret_cast<const __half*>(d.embed);
     const int64_t* x_token = d.token;  // layer 0 reads the embedding row of *token
@@ -185,7 +272,9 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.K = d.hidden;
             p.group_size = d.group_size;
             p.y = s->qkv;
-            if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
+            p.err_flag = s->err_flag;
+            if (!(g_step_skip_mask & 1))
+                if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
         }
         // K2: attention with fused q/k norm, RoPE, KV write
         {
@@ -219,7 +308,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.part = s->attn_part;
             p.counters = s->attn_counters;
             p.err_flag = s->err_flag;
-            if (int rc = launch_attn_decode(p, d.kv_int8 != 0, true, lc)) return rc;
+            if (!(g_step_skip_mask & 2))
+                if (int rc = launch_attn_decode(p, d.kv_int8 != 0, true, lc)) return rc;
         }
         // K3: x1 = x_prev + W8(o) . attn
         {
@@ -231,9 +321,11 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.K = A;
             p.group_size = d.group_size;
             p.y = s->xa;
+            p.err_flag = s->err_flag;
             p.resid = x_prev;
             p.resid_token = x_token;
-            if (int rc = launch_gemv_w8(p, 1, false, true, false, lc)) return rc;
+            if (!(g_step_skip_mask & 4))
+                if (int rc = launch_gemv_w8(p, 1, false, true, false, lc)) return rc;
         }
         // K4: h2 = RMSNorm(x1); router logits, softmax, top-k
         {
@@ -251,7 +343,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.top_w = s->top_w;
             p.top_i = s->top_i + static_cast<int64_t>(l) * d.top_k;
             p.counter = s->route_counter;
-            if (int rc = launch_route(p, true, lc)) return rc;
+            if (!(g_step_skip_mask & 8))
+                if (int rc = launch_route(p, true, lc)) return rc;
         }
         // K5 + K6: grouped experts, x2 = x1 + moe
         {
@@ -273,8 +366,10 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.out = s->xb;
             p.resid = s->xa;
             p.err_flag = s->err_flag;
-            if (int rc = launch_moe_gate_up(p, true, lc)) return rc;
-            if (int rc = launch_moe_down(p, true, lc)) return rc;
+            if (!(g_step_skip_mask & 16))
+                if (int rc = launch_moe_gate_up(p, true, lc)) return rc;
+            if (!(g_step_skip_mask & 32))
+                if (int rc = launch_moe_down(p, true, lc)) return rc;
         }
         x_prev = s->xb;
         x_token = nullptr;
@@ -292,7 +387,9 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.K = d.hidden;
         p.group_size = d.group_size;
         p.y = d.logits;
-        if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
+        p.err_flag = s->err_flag;
+        if (!(g_step_skip_mask & 64))
+            if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
     }
     if (launches) *launches = count;
     return LEMOQ_OK;

@@ -1,0 +1,49 @@
+// Parameter block of the whole-step cooperative kernel (step_mega.cu), shared with the step engine.
+#pragma once
+
+#include "kernels.h"
+
+namespace lemoq {
+
+struct MegaLayer {
+    const __half *ln1, *ln2, *q_norm, *k_norm;
+    const int8_t* qkv_codes;
+    const __half* qkv_scale;
+    const int8_t* o_codes;
+    const __half* o_scale;
+    const __half* router;
+    const int8_t* gu_codes;
+    const __half* gu_scale;
+    const int8_t* dn_codes;
+    const __half* dn_scale;
+    __half *keys, *values;
+    int8_t* kc;
+    __half* ks;
+    int8_t* vc;
+    __half* vs;
+};
+
+struct MegaParams {
+    int layers, H, heads, D, E, K, F, V, group, S, splits, kv_int8, norm_topk;
+    float eps, qk_scale_log2;
+    const __half *embed, *final_norm, *lm_scale, *rope_cos, *rope_sin;
+    const int8_t* lm_codes;
+    const int64_t *token, *cache_position;
+    const int32_t* filled;
+    __half* logits;
+    const MegaLayer* L;  // device array
+    int* err_flag;
+    unsigned int *bar_counter, *bar_epoch, *attn_counters;
+    __half *qkv, *attn, *xa, *xb, *act, *router_logits, *top_w;
+    int64_t* top_i;
+    float* attn_part;
+    int barriers_per_launch;
+    unsigned long long* stamps;  // optional: 6*layers + 2 phase time stamps of the last step
+};
+
+size_t mega_smem_bytes();
+bool mega_eligible(const lemoq_step_desc& d);
+int mega_grid(const lemoq_step_desc& d, int splits);  // blocks to launch (one per SM), 0 = unavailable
+int launch_step_mega(const MegaParams& p, int grid, cudaStream_t stream);
+
+}  // namespace lemoq

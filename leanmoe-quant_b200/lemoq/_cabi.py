@@ -46,6 +46,7 @@ class StepDesc(Structure):
 _SIGNATURES = {
     "lemoq_version": (c_char_p, []),
     "lemoq_last_error": (c_char_p, []),
+    "lemoq_set_tuning": (c_int, [c_int, c_int]),
     "lemoq_rtn_quantize_w8": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "lemoq_dequant_gemv_w8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "lemoq_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
@@ -81,6 +82,7 @@ _SIGNATURES = {
     "lemoq_step_error_flag": (c_void_p, [c_void_p]),
     "lemoq_step_topk_ids": (c_void_p, [c_void_p]),
     "lemoq_step_router_logits": (c_void_p, [c_void_p]),
+    "lemoq_step_phase_stamps": (c_void_p, [c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(sorted(_SIGNATURES))
