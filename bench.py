@@ -401,9 +401,15 @@ def main() -> int:
     ap.add_argument("--engine", default="auto", choices=["auto", "step", "ops"])
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--step-kernel", default="default", choices=["default", "chained", "whole"],
+                    help="step engine: chained kernels with PDL, or the single cooperative whole-step kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.step_kernel != "default":
+        from lemoq import _cabi
+
+        _cabi.call("lemoq_set_tuning", 4, 1 if args.step_kernel == "whole" else 0)
     return run_gpu(args)
 
 

@@ -14,6 +14,9 @@
 #include <new>
 
 #include "kernels.h"
+#include <cstdio>
+#include <cstdlib>
+
 #include "step_mega.h"
 
 struct lemoq_step {
@@ -92,8 +95,8 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(attn_part, float*, sizeof(float) * d.heads * splits * (d.head_dim + 2));
     LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
-    LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * d.layers);
-    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2));
+    LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * (d.layers + 1));
+    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 64));
 #undef LEMOQ_TAKE
     return c.off;
 }
@@ -122,6 +125,7 @@ static int validate(const lemoq_step_desc& d) {
 
 namespace lemoq {
 int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
+int g_mega_depth = 8;      // lemoq_set_tuning key 5: stages a warp of the whole-step kernel keeps in flight (capped by its ring)
 int g_step_use_mega = 0;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
 }
 
@@ -160,15 +164,17 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
     s->splits = splits;
     carve(*desc, splits, s);
     s->mega_grid = 0;
+    if (g_step_use_mega && getenv("LEMOQ_VERBOSE")) fprintf(stderr, "lemoq: whole-step kernel eligible: %d\n", (int)mega_eligible(*desc));
     if (g_step_use_mega && mega_eligible(*desc)) {
         const int grid = mega_grid(*desc, splits);
         if (grid > 0) {
             // attention units are (head, split) blocks: at most one per resident block
             int ms = grid / desc->heads;
             if (ms < 1) ms = 1;
+            if (ms > 9) ms = 9;  // the split merge of the whole-step kernel is unrolled for 9
             if (desc->attn_splits > 0 && desc->attn_splits < ms) ms = desc->attn_splits;
             if (desc->heads * ms <= grid && ms <= splits) {
-                MegaLayer* host = new (std::nothrow) MegaLayer[desc->layers];
+                MegaLayer* host = new (std::nothrow) MegaLayer[desc->layers + 1]();
                 if (host) {
                     for (int l = 0; l < desc->layers; ++l) {
                         const lemoq_layer_desc& L = layers[l];
@@ -193,8 +199,12 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
                         m.vc = L.vc;
                         m.vs = reinterpret_cast<__half*>(L.vs);
                     }
+                    // pseudo layer after the last one: the lm_head rows stream like q.k.v rows behind the final norm
+                    host[desc->layers].ln1 = reinterpret_cast<const __half*>(desc->final_norm);
+                    host[desc->layers].qkv_codes = desc->lm_head_codes;
+                    host[desc->layers].qkv_scale = reinterpret_cast<const __half*>(desc->lm_head_scale);
                     // set-up time only: the descriptors move to the device once (synchronous copy)
-                    const cudaError_t err = cudaMemcpy(s->mega_layers, host, sizeof(MegaLayer) * desc->layers, cudaMemcpyHostToDevice);
+                    const cudaError_t err = cudaMemcpy(s->mega_layers, host, sizeof(MegaLayer) * (desc->layers + 1), cudaMemcpyHostToDevice);
                     delete[] host;
                     if (err == cudaSuccess) {
                         s->mega_grid = grid;
@@ -250,6 +260,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.router_logits = s->router_logits; p.top_w = s->top_w; p.top_i = s->top_i; p.attn_part = s->attn_part;
         p.barriers_per_launch = 6 * d.layers + 1;
         p.stamps = s->stamps;
+        p.depth = g_mega_depth;
         if (int rc = launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream))) return rc;
         if (launches) *launches = 1;
         return LEMOQ_OK;

@@ -3,38 +3,45 @@
 // Why: on B200 a dependent global-memory round trip costs ~0.7 us and a kernel boundary inside a
 // graph 3-5 us, while a whole layer of the step only streams ~11 us worth of bytes.  With six
 // all-to-all dependencies per layer, separate kernels spend most of the step waiting.  Here one
-// block per SM stays resident for the whole step; the six phases of a layer are separated by a
-// grid barrier (~1.2 us), and every warp keeps a private ring of shared-memory stages that it
-// fills with bulk asynchronous copies IN PROGRAM ORDER ACROSS PHASES: while a warp waits at a
-// barrier the weights of its next tasks (q.k.v, o_proj, router and lm_head rows do not depend
-// on activations) are already streaming in.  Only the expert rows have to wait for the routing.
+// block per SM stays resident for the whole step; the phases of a layer are separated by a grid
+// barrier (~1.2 us), and every warp keeps a private ring of shared-memory stages that it fills
+// with bulk asynchronous copies IN PROGRAM ORDER ACROSS PHASES: while a warp waits at a barrier the
+// weights of its next tasks (q.k.v, o_proj, router and lm_head rows do not depend on activations)
+// are already streaming in.  Only the expert rows have to wait for the routing.
+//
+// Arithmetic of the W8 rows: the activation vector of a phase is converted once per block into
+// three planes of signed 7-bit digits (x = sx * (d2*2^14 + d1*2^7 + d0), sx a power of two chosen
+// per 16-element lane chunk, so fp16 activations within 2^9 of the chunk maximum are represented
+// exactly and the rest to 2^-20 of it); the int8 weight codes are then consumed as they are by the
+// integer dot-product instruction (dp4a), 12 per 16 codes, with exact int32 partial sums that are
+// combined and scaled in fp32.  No int8->float conversion of the weights takes place.
 //
 // Phases per layer (all blocks take part in each):
-//   A  q.k.v rows          x = RMSNorm(x_prev)                         -> qkv
-//   B  attention           one (head, split) per block, fused q/k norm + RoPE + KV write; the last
-//                          block of a head merges the splits              -> attn
-//   C  o_proj rows         + residual                                     -> x1
-//   D  router rows (fp16)  h2 = RMSNorm(x1)                               -> router logits
+//   A  q.k.v rows          x = RMSNorm(x_prev)                                   -> qkv
+//   B  attention           one (head, split) per block; fused q/k norm + RoPE + KV write   -> partials
+//   C  o_proj rows         every block merges the attention partials itself; + residual -> x1
+//   D  router rows (fp16)  h2 = RMSNorm(x1) (kept in shared memory for E)        -> router logits
 //   E  expert gate/up      every warp derives the top-k itself from the logits; SwiGLU -> act
-//   F  expert down         routing-weighted sum + residual                -> x2
+//   F  expert down         routing-weighted sum + residual                        -> x2
 // then the lm_head rows on RMSNorm(x2).
-//
-// Numerics are those of the separate kernels (same rounding points, same reduction orders).
+#include <cstddef>
+#include <cstdio>
+#include <cstdlib>
+
 #include "step_mega.h"
-#include "stream_gemv.cuh"
+#include "stream.cuh"
 
 namespace lemoq {
 
-constexpr int kMegaWarps = 12;
+constexpr int kMegaWarps = 14;
 constexpr int kMegaThreads = kMegaWarps * 32;
-constexpr int kMegaStages = 4;
+constexpr int kMegaStages = 3;
 constexpr int kMegaStageBytes = 4224;  // 2 rows x 2048 codes + 2 x 32 bytes of scales, padded to 128
-constexpr int kMegaScratchBytes = 16384;
-constexpr int kMegaMode = DOT_F16_FOLD;
+constexpr int kMegaScratchBytes = 28672;
 constexpr int NCH = 4;  // activations up to 2048 wide
+constexpr int kMaxSplits = 9;   // attention splits per head the merge is unrolled for
 constexpr uint32_t kBarrierSpinLimit = 1u << 24;
 
-enum Phase : int { PH_A = 0, PH_C = 1, PH_D = 2, PH_E = 3, PH_F = 4, PH_LM = 5, PH_END = 6 };
 
 // ---------------------------------------------------------------------------------------------
 // grid barrier: monotonically increasing arrival counter, wrap-safe comparison, bounded spin
@@ -70,257 +77,316 @@ struct GridBarrier {
     }
 };
 
+// Phase time stamps (block 0, thread 0; nanoseconds of the global timer) for profiling the step.
+__device__ __forceinline__ void stamp(const MegaParams& p, int slot) {
+    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.stamps[slot] = t;
+    }
+}
+
+// Finer stamps of layer 1 only (64 extra slots after the phase stamps), for profiling.
+__device__ __forceinline__ void substamp(const MegaParams& p, int l, int idx) {
+    if (p.stamps != nullptr && l == 1 && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.stamps[6 * p.layers + 2 + idx] = t;
+    }
+}
+
+// SM cycle counter of block 0 / thread 0 into the extra stamp slots 32.. (profiling; last writer wins).
+__device__ __forceinline__ void dbg_clock(const MegaParams& p, int idx) {
+    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[6 * p.layers + 2 + 32 + idx] = clock64();
+}
+
+// ---------------------------------------------------------------------------------------------
+// activation vectors as digit planes in shared memory
+// ---------------------------------------------------------------------------------------------
+// Layout of one quantised vector of up to NV lane chunks (a lane chunk = 16 consecutive elements;
+// chunk index lc = k / 16): plane p word w of lane chunk lc at ((p * nlc + lc) * 4 + w) words; the
+// chunk scales follow as floats.  A lane reads its chunk of a plane with one 128-bit load.
+
+// Four activations (fp32 holding fp16-representable values) -> one packed word per plane.  `inv` is
+// the exact power-of-two reciprocal of the chunk scale.  X = round(f * inv) (|X| < 2^20) is split in
+// two's complement: X = d2 * 2^14 + d1 * 2^7 + d0 with d0, d1 in [0, 127] and d2 in [-64, 63].
+__device__ __forceinline__ void quantise4(const float (&f)[4], float inv, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
+    uint32_t X[4], Y[4], Z[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        // round to nearest even through the 1.5 * 2^23 offset: the integer sits in the low mantissa bits
+        X[j] = __float_as_uint(fmaf(f[j], inv, 12582912.0f)) - 0x4B400000u;
+        Y[j] = X[j] >> 7;
+        Z[j] = static_cast<uint32_t>(static_cast<int>(X[j]) >> 14);
+    }
+    w0 = __byte_perm(__byte_perm(X[0], X[1], 0x0040), __byte_perm(X[2], X[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    w1 = __byte_perm(__byte_perm(Y[0], Y[1], 0x0040), __byte_perm(Y[2], Y[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    w2 = __byte_perm(__byte_perm(Z[0], Z[1], 0x0040), __byte_perm(Z[2], Z[3], 0x0040), 0x5410);
+}
+// Chunk scale sx = 2^(floor(log2(amax)) - 19) (1 for an all-zero chunk) and its reciprocal.
+__device__ __forceinline__ void chunk_scale(float amax, float& sx, float& inv) {
+    const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);  // biased exponent
+    if (amax > 0.f && e > 20) {
+        sx = __uint_as_float(static_cast<uint32_t>(e - 19) << 23);
+        inv = __uint_as_float(static_cast<uint32_t>(254 - (e - 19)) << 23);
+    } else {  // zero or denormal-range chunk: fixed tiny scale keeps the arithmetic exact
+        sx = __uint_as_float(static_cast<uint32_t>(2) << 23);
+        inv = __uint_as_float(static_cast<uint32_t>(252) << 23);
+    }
+}
+
+// One 4-element item of a vector of nlc lane chunks: four consecutive threads share a lane chunk, whole
+// warps call this together (threads whose item lies past the end pass on = false and zeros).
+__device__ __forceinline__ void quantise_item(uint32_t* dst, int nlc, int item, bool on, const float (&f)[4]) {
+    float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float sx, inv;
+    chunk_scale(amax, sx, inv);
+    uint32_t w0, w1, w2;
+    quantise4(f, inv, w0, w1, w2);
+    if (on) {
+        const int lc = item >> 2, w = item & 3;
+        dst[(0 * nlc + lc) * 4 + w] = w0;
+        dst[(1 * nlc + lc) * 4 + w] = w1;
+        dst[(2 * nlc + lc) * 4 + w] = w2;
+        if (w == 0) reinterpret_cast<float*>(dst + 3 * nlc * 4)[lc] = sx;
+    }
+}
+
+// R W8 rows (codes and per-group scales in shared memory) against a quantised vector in shared memory:
+// per-lane partial sums.  Lane `lane` owns the lane chunks c*32 + lane, i.e. codes c*512 + lane*16 .. +15.
+template <int R>
+__device__ __forceinline__ void dp_rows(float (&acc)[R], const unsigned char* const (&row)[R], const __half* const (&sc)[R],
+                                        const uint32_t* __restrict__ xq, int K, int lane, int sbase, int sstride) {
+    const int nlc = K >> 4;
+    const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+        const int lc = c * 32 + lane;
+        if (lc < nlc) {
+            const uint4 x0 = *reinterpret_cast<const uint4*>(xq + (0 * nlc + lc) * 4);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xq + (1 * nlc + lc) * 4);
+            const uint4 x2 = *reinterpret_cast<const uint4*>(xq + (2 * nlc + lc) * 4);
+            const float sx = sxs[lc];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint4 w = *reinterpret_cast<const uint4*>(row[r] + lc * 16);
+                int s0 = __dp4a(static_cast<int>(w.x), static_cast<int>(x0.x), 0);
+                int s1 = __dp4a(static_cast<int>(w.x), static_cast<int>(x1.x), 0);
+                int s2 = __dp4a(static_cast<int>(w.x), static_cast<int>(x2.x), 0);
+                s0 = __dp4a(static_cast<int>(w.y), static_cast<int>(x0.y), s0);
+                s1 = __dp4a(static_cast<int>(w.y), static_cast<int>(x1.y), s1);
+                s2 = __dp4a(static_cast<int>(w.y), static_cast<int>(x2.y), s2);
+                s0 = __dp4a(static_cast<int>(w.z), static_cast<int>(x0.z), s0);
+                s1 = __dp4a(static_cast<int>(w.z), static_cast<int>(x1.z), s1);
+                s2 = __dp4a(static_cast<int>(w.z), static_cast<int>(x2.z), s2);
+                s0 = __dp4a(static_cast<int>(w.w), static_cast<int>(x0.w), s0);
+                s1 = __dp4a(static_cast<int>(w.w), static_cast<int>(x1.w), s1);
+                s2 = __dp4a(static_cast<int>(w.w), static_cast<int>(x2.w), s2);
+                const float t = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
+                acc[r] = fmaf(t, sx * __half2float(sc[r][c * sstride + sbase]), acc[r]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // per-warp task stream: the order in which a warp will consume weight tasks over the whole step
 // ---------------------------------------------------------------------------------------------
-struct Cursor {
-    int layer, phase, i, slot;
+// Task kinds and what one stage holds (K = input width of the rows):
+//   KIND_A  q.k.v rows (and the lm_head rows, as the q.k.v of a pseudo layer): two consecutive rows
+//           [codes 2*K][scales 2*(K/group) halves]
+//   KIND_C  o_proj rows, same layout
+//   KIND_D  one fp16 router row [2*K]
+//   KIND_E  gate row n and up row n of one routed expert [gate K][up K][gate scales][up scales]
+//   KIND_F  down row n of `sps` consecutive routed experts [codes sps*F][scales sps*(F/group) halves]
+// Every bulk copy of a kind is described by one CopyDesc in shared memory; lane c of the warp issues
+// copy c, so the issue path is a handful of instructions whatever the kind.
+enum Kind : int { KIND_A = 0, KIND_C = 1, KIND_D = 2, KIND_E = 3, KIND_F = 4, KIND_END = 5 };
+
+struct CopyDesc {
+    uint32_t field;     // byte offset of the source base pointer inside MegaLayer
+    uint32_t bytes;     // size of the copy
+    uint32_t dst;       // byte offset inside the stage
+    uint32_t t_stride;  // source bytes per task index (row index n for E and F)
+    uint32_t e_stride;  // source bytes per expert
+    uint32_t cst;       // constant source offset
+    uint32_t pad0, pad1;
 };
+struct StreamTable {
+    CopyDesc copy[5][4];
+    uint32_t ncopies[5];
+    uint32_t tx[5];
+};
+
+#define LEMOQ_FIELD(name) static_cast<uint32_t>(offsetof(MegaLayer, name))
+
+__device__ __forceinline__ void build_stream_table(StreamTable& t, const MegaParams& p, int sps) {
+    const uint32_t H = p.H, A = p.heads * p.D, F = p.F, g = p.group;
+    auto set = [&](int kind, int c, uint32_t field, uint32_t bytes, uint32_t dst, uint32_t ts, uint32_t es, uint32_t cst) {
+        t.copy[kind][c] = CopyDesc{field, bytes, dst, ts, es, cst, 0u, 0u};
+    };
+    set(KIND_A, 0, LEMOQ_FIELD(qkv_codes), 2 * H, 0, 2 * H, 0, 0);
+    set(KIND_A, 1, LEMOQ_FIELD(qkv_scale), 4 * (H / g), 2 * H, 4 * (H / g), 0, 0);
+    t.ncopies[KIND_A] = 2;
+    t.tx[KIND_A] = 2 * H + 4 * (H / g);
+    set(KIND_C, 0, LEMOQ_FIELD(o_codes), 2 * A, 0, 2 * A, 0, 0);
+    set(KIND_C, 1, LEMOQ_FIELD(o_scale), 4 * (A / g), 2 * A, 4 * (A / g), 0, 0);
+    t.ncopies[KIND_C] = 2;
+    t.tx[KIND_C] = 2 * A + 4 * (A / g);
+    set(KIND_D, 0, LEMOQ_FIELD(router), 2 * H, 0, 2 * H, 0, 0);
+    t.ncopies[KIND_D] = 1;
+    t.tx[KIND_D] = 2 * H;
+    const uint32_t sb = 2 * (H / g);
+    set(KIND_E, 0, LEMOQ_FIELD(gu_codes), H, 0, H, 2 * F * H, 0);
+    set(KIND_E, 1, LEMOQ_FIELD(gu_codes), H, H, H, 2 * F * H, F * H);
+    set(KIND_E, 2, LEMOQ_FIELD(gu_scale), sb, 2 * H, sb, 2 * F * sb, 0);
+    set(KIND_E, 3, LEMOQ_FIELD(gu_scale), sb, 2 * H + sb, sb, 2 * F * sb, F * sb);
+    t.ncopies[KIND_E] = 4;
+    t.tx[KIND_E] = 2 * H + 2 * sb;
+    const uint32_t gb = 2 * (F / g);
+    set(KIND_F, 0, LEMOQ_FIELD(dn_codes), F, 0, F, H * F, 0);
+    set(KIND_F, 1, LEMOQ_FIELD(dn_scale), gb, sps * F, gb, H * gb, 0);
+    t.ncopies[KIND_F] = 2;  // per routed expert of the stage
+    t.tx[KIND_F] = F + gb;  // per routed expert of the stage
+}
 
 struct WarpStream {
     const MegaParams* P;
+    const StreamTable* T;
     WarpRing<kMegaStages> ring;
     const unsigned char* my;  // generic pointer to this warp's stage 0
     int wg, G, lane;
-    int n_issued, n_consumed;
-    int ids_ready_layer;  // expert tasks of layers <= this may be issued
-    long long ids_reg;    // lane k holds the k-th expert id of ids_ready_layer
-    Cursor cur;
+    int cnt[5];               // tasks of this warp per kind in a layer
+    int cnt_lm;               // lm_head tasks of this warp
+    int sps;                  // routed experts per stage in kind F
+    int inflight;             // stages issued and not yet released
+    int depth;                // upper bound of inflight
+    int i_stage;              // next stage to fill
+    int c_stage, c_par;       // next stage to consume and its barrier parity
+    int ids_ready_layer;      // expert tasks of layers <= this may be issued
+    int ids_reg;              // lane k holds the k-th expert id of ids_ready_layer
+    // issue cursor: layer, kind, tasks left in the kind, task index, routed-expert slot, row inside the expert (E)
+    int c_layer, c_kind, c_left, c_task, c_slot, c_n;
 
     __device__ __forceinline__ int count(int n) const { return n > wg ? (n - wg + G - 1) / G : 0; }
-    __device__ __forceinline__ int phase_count(int phase) const {
-        const MegaParams& p = *P;
-        switch (phase) {
-            case PH_A: return count(3 * p.heads * p.D / 2);
-            case PH_C: return count(p.H / 2);
-            case PH_D: return count(p.E);
-            case PH_E: return count(p.K * p.F);
-            case PH_F: return count(p.H / 2);
-            default: return count(p.V / 2);
-        }
+    __device__ __forceinline__ int kind_cnt(int k) const {
+        int v = cnt[0];
+#pragma unroll
+        for (int i = 1; i < 5; ++i) v = k == i ? cnt[i] : v;
+        return v;
     }
-    // move the cursor to the next valid task (or PH_END)
-    __device__ __forceinline__ void normalise() {
-        const MegaParams& p = *P;
-        while (cur.phase != PH_END) {
-            if (cur.i < phase_count(cur.phase)) return;
-            cur.i = 0;
-            cur.slot = 0;
-            if (cur.phase == PH_LM) {
-                cur.phase = PH_END;
-            } else if (cur.phase == PH_F) {
-                ++cur.layer;
-                cur.phase = cur.layer < p.layers ? PH_A : PH_LM;
-            } else {
-                ++cur.phase;
+    __device__ __forceinline__ void enter_kind() {  // position the cursor on the first task of c_kind
+        c_task = wg;
+        c_slot = 0;
+        c_n = wg;
+        if (c_kind == KIND_E) {
+            while (c_n >= P->F) {
+                c_n -= P->F;
+                ++c_slot;
             }
         }
+    }
+    __device__ __forceinline__ void next_kind() {
+        do {
+            if (c_layer == P->layers) {  // the pseudo layer only has the lm_head rows
+                c_kind = KIND_END;
+                return;
+            }
+            if (c_kind == KIND_F) {
+                c_kind = KIND_A;
+                ++c_layer;
+            } else {
+                ++c_kind;
+            }
+            c_left = c_layer == P->layers ? cnt_lm : kind_cnt(c_kind);
+        } while (c_left == 0);
+        enter_kind();
+    }
+    __device__ __forceinline__ void start() {
+        c_layer = 0;
+        c_kind = KIND_A;
+        c_left = cnt[KIND_A];
+        if (c_left == 0) next_kind();
+        else enter_kind();
     }
     __device__ __forceinline__ void advance() {
-        if (cur.phase == PH_F) {
-            if (++cur.slot < P->K) return;
-            cur.slot = 0;
+        if (c_kind == KIND_F) {
+            c_slot += sps;
+            if (c_slot < P->K) return;
+            c_slot = 0;
+        } else if (c_kind == KIND_E) {
+            c_n += G;
+            while (c_n >= P->F) {
+                c_n -= P->F;
+                ++c_slot;
+            }
         }
-        ++cur.i;
-        normalise();
+        c_task += G;
+        if (--c_left == 0) next_kind();
     }
     __device__ __forceinline__ bool allowed() const {
-        if (cur.phase == PH_END) return false;
-        if (cur.phase == PH_E || cur.phase == PH_F) return cur.layer <= ids_ready_layer;
-        return true;
-    }
-    // lane 0: enqueue the copies of the cursor's task into stage s
-    __device__ __forceinline__ void issue(int s, int expert) {
-        const MegaParams& p = *P;
-        const MegaLayer& L = p.L[cur.layer < p.layers ? cur.layer : 0];
-        const int task = wg + cur.i * G;
-        const uint32_t dst = ring.stage(s), bar = ring.bar(s);
-        const int A = p.heads * p.D;
-        switch (cur.phase) {
-            case PH_A: {
-                const int g = p.H / p.group;
-                const uint32_t cb = 2 * p.H, sb = 2 * g * 2;
-                mbar_expect_tx(bar, cb + sb);
-                bulk_g2s(dst, L.qkv_codes + static_cast<int64_t>(task) * 2 * p.H, cb, bar);
-                bulk_g2s(dst + cb, L.qkv_scale + static_cast<int64_t>(task) * 2 * g, sb, bar);
-                break;
-            }
-            case PH_C: {
-                const int g = A / p.group;
-                const uint32_t cb = 2 * A, sb = 2 * g * 2;
-                mbar_expect_tx(bar, cb + sb);
-                bulk_g2s(dst, L.o_codes + static_cast<int64_t>(task) * 2 * A, cb, bar);
-                bulk_g2s(dst + cb, L.o_scale + static_cast<int64_t>(task) * 2 * g, sb, bar);
-                break;
-            }
-            case PH_D: {
-                const uint32_t cb = 2 * p.H;
-                mbar_expect_tx(bar, cb);
-                bulk_g2s(dst, L.router + static_cast<int64_t>(task) * p.H, cb, bar);
-                break;
-            }
-            case PH_E: {
-                const int g = p.H / p.group;
-                const int slot = task / p.F, n = task - slot * p.F;
-                (void)slot;
-                const int64_t rg = static_cast<int64_t>(expert) * 2 * p.F + n, ru = rg + p.F;
-                const uint32_t rb = p.H, sb = g * 2;
-                mbar_expect_tx(bar, 2 * rb + 2 * sb);
-                bulk_g2s(dst, L.gu_codes + rg * p.H, rb, bar);
-                bulk_g2s(dst + rb, L.gu_codes + ru * p.H, rb, bar);
-                bulk_g2s(dst + 2 * rb, L.gu_scale + rg * g, sb, bar);
-                bulk_g2s(dst + 2 * rb + sb, L.gu_scale + ru * g, sb, bar);
-                break;
-            }
-            case PH_F: {
-                const int g = p.F / p.group;
-                const int64_t row = static_cast<int64_t>(expert) * p.H + 2 * task;
-                const uint32_t cb = 2 * p.F, sb = 2 * g * 2;
-                mbar_expect_tx(bar, cb + sb);
-                bulk_g2s(dst, L.dn_codes + row * p.F, cb, bar);
-                bulk_g2s(dst + cb, L.dn_scale + row * g, sb, bar);
-                break;
-            }
-            default: {
-                const int g = p.H / p.group;
-                const uint32_t cb = 2 * p.H, sb = 2 * g * 2;
-                mbar_expect_tx(bar, cb + sb);
-                bulk_g2s(dst, p.lm_codes + static_cast<int64_t>(task) * 2 * p.H, cb, bar);
-                bulk_g2s(dst + cb, p.lm_scale + static_cast<int64_t>(task) * 2 * g, sb, bar);
-                break;
-            }
-        }
+        if (c_kind == KIND_END) return false;
+        return c_kind < KIND_E || c_layer <= ids_ready_layer;
     }
     // keep the ring full (called by the whole warp)
     __device__ __forceinline__ void pump() {
-        while (n_issued - n_consumed < kMegaStages && allowed()) {
-            int expert = 0;
-            if (cur.phase == PH_E) {
-                expert = static_cast<int>(__shfl_sync(0xffffffffu, ids_reg, (wg + cur.i * G) / P->F));
-            } else if (cur.phase == PH_F) {
-                expert = static_cast<int>(__shfl_sync(0xffffffffu, ids_reg, cur.slot));
+        while (inflight < depth && allowed()) {
+            const uint32_t dst = ring.stage(i_stage), bar = ring.bar(i_stage);
+            const bool isF = c_kind == KIND_F;
+            const int nsl = isF ? min(sps, P->K - c_slot) : 1;
+            const int j = isF ? lane >> 1 : 0;       // routed expert of the stage this lane copies for
+            const int ci = isF ? lane & 1 : lane;    // which copy of the kind
+            const int expert = __shfl_sync(0xffffffffu, ids_reg, (c_slot + j) & 31);
+            if (lane == 0) mbar_expect_tx(bar, T->tx[c_kind] * nsl);
+            __syncwarp();
+            if (lane < static_cast<int>(T->ncopies[c_kind]) * nsl) {
+                const CopyDesc d = T->copy[c_kind][ci];
+                const char* base = *reinterpret_cast<const char* const*>(reinterpret_cast<const char*>(P->L + c_layer) + d.field);
+                const uint32_t t = c_kind == KIND_E ? c_n : c_task;
+                const uint64_t off = static_cast<uint64_t>(c_kind >= KIND_E ? expert : 0) * d.e_stride +
+                                     static_cast<uint64_t>(t) * d.t_stride + d.cst;
+                bulk_g2s(dst + d.dst + j * d.bytes, base + off, d.bytes, bar);
             }
-            if (lane == 0) issue(n_issued % kMegaStages, expert);
-            ++n_issued;
+            i_stage = i_stage + 1 == kMegaStages ? 0 : i_stage + 1;
+            ++inflight;
             advance();
         }
     }
     // wait for the oldest stage; returns its generic address (nullptr on timeout)
     __device__ __forceinline__ const unsigned char* acquire() {
-        const int s = n_consumed % kMegaStages;
-        if (!mbar_wait(ring.bar(s), (n_consumed / kMegaStages) & 1)) {
+        if (!mbar_wait(ring.bar(c_stage), c_par)) {
             if (P->err_flag && lane == 0) atomicOr(P->err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
             return nullptr;
         }
-        return my + static_cast<size_t>(s) * kMegaStageBytes;
+        return my + static_cast<size_t>(c_stage) * kMegaStageBytes;
     }
     __device__ __forceinline__ void release() {
         __syncwarp();
-        ++n_consumed;
+        if (++c_stage == kMegaStages) {
+            c_stage = 0;
+            c_par ^= 1;
+        }
+        --inflight;
         pump();
     }
 };
 
 // ---------------------------------------------------------------------------------------------
-// row dot product with the lane layout derived on the fly (group_size divides 512)
+// routing: every warp derives softmax + top-k from the E fp16 logits (E <= 128), identically.
+// Probabilities are positive floats, so their bit patterns order like unsigned integers: a warp-wide
+// integer maximum plus a ballot gives the largest probability and its lowest index per round.
 // ---------------------------------------------------------------------------------------------
-struct LaneLite {
-    int lane16;   // lane * 16: byte offset of the lane inside a 512-byte chunk
-    int sbase;    // scale index of the lane inside a chunk
-    int sstride;  // scales per chunk
+struct TopK {
+    int id;   // lane k: k-th expert id
+    float w;  // lane k: its routing weight (fp16-rounded)
 };
-__device__ __forceinline__ float row_dot(const unsigned char* __restrict__ row, const __half* __restrict__ scales, int K,
-                                         const LaneLite& ll, const XSlice<NCH, kMegaMode>& xs) {
-    float acc = 0.f;
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-        const int k0 = c * 512 + ll.lane16;
-        if (k0 < K) {
-            const uint4 w = *reinterpret_cast<const uint4*>(row + k0);
-            acc = fmaf(xs.dot(c, w), __half2float(scales[c * ll.sstride + ll.sbase]), acc);
-        }
-    }
-    return acc;
-}
-
-// Activation slice loaders that convert chunk by chunk (low register peak).
-__device__ __forceinline__ void slice_plain(XSlice<NCH, kMegaMode>& xs, const __half* __restrict__ x, int K, int lane16) {
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-        const int k0 = c * 512 + lane16;
-        float f[16];
-        if (k0 < K) {
-            unpack8_h(ld_cg16(x + k0), &f[0]);
-            unpack8_h(ld_cg16(x + k0 + 8), &f[8]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = 0.f;
-        }
-        xs.set(c, f);
-    }
-}
-// Raw row words of the lane plus the RMSNorm statistic (every warp covers the row exactly once).
-struct RawRow {
-    uint4 w[NCH][2];
-    float rstd;
-    __device__ __forceinline__ void load(const __half* __restrict__ x, int K, int lane16, float eps) {
-        float ss = 0.f;
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-            const int k0 = c * 512 + lane16;
-            if (k0 < K) {
-                w[c][0] = ld_cg16(x + k0);
-                w[c][1] = ld_cg16(x + k0 + 8);
-                float f[16];
-                unpack8_h(w[c][0], &f[0]);
-                unpack8_h(w[c][1], &f[8]);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) ss = fmaf(f[j], f[j], ss);
-            } else {
-                w[c][0] = w[c][1] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        ss = warp_sum(ss);
-        rstd = 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
-    }
-    // normalised values of chunk c (HF rounding chain), as fp32
-    __device__ __forceinline__ void chunk(int c, const __half* __restrict__ nw, int K, int lane16, float (&f)[16]) const {
-        const int k0 = c * 512 + lane16;
-        if (k0 < K) {
-            const uint4 wa = *reinterpret_cast<const uint4*>(nw + k0);
-            const uint4 wb = *reinterpret_cast<const uint4*>(nw + k0 + 8);
-            const __half* xh0 = reinterpret_cast<const __half*>(&w[c][0]);
-            const __half* xh1 = reinterpret_cast<const __half*>(&w[c][1]);
-            const __half* wh0 = reinterpret_cast<const __half*>(&wa);
-            const __half* wh1 = reinterpret_cast<const __half*>(&wb);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                f[j] = norm_elem(xh0[j], rstd, wh0[j]);
-                f[8 + j] = norm_elem(xh1[j], rstd, wh1[j]);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) f[j] = 0.f;
-        }
-    }
-};
-__device__ __forceinline__ void slice_norm(XSlice<NCH, kMegaMode>& xs, const __half* __restrict__ x,
-                                           const __half* __restrict__ nw, float eps, int K, int lane16) {
-    RawRow r;
-    r.load(x, K, lane16, eps);
-#pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-        float f[16];
-        r.chunk(c, nw, K, lane16, f);
-        xs.set(c, f);
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// routing: every warp derives softmax + top-k from the E fp16 logits (E <= 128), identically
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void warp_topk(const __half* __restrict__ logits, int E, int K, bool norm, int lane,
-                                          long long& id_reg, float& w_reg) {
+__device__ __noinline__ TopK warp_topk(const __half* __restrict__ logits, int E, int K, bool norm, int lane) {
+    int id_reg;
+    float w_reg;
     float v[4];
     float mx = -INFINITY;
 #pragma unroll
@@ -338,30 +404,22 @@ __device__ __forceinline__ void warp_topk(const __half* __restrict__ logits, int
         sum += v[j];
     }
     sum = warp_sum(sum);
+    unsigned int key[4];  // bits of the probability + 1; 0 = absent or already taken
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = (lane + 32 * j) < E ? v[j] / sum : -1.0e30f;
+    for (int j = 0; j < 4; ++j) key[j] = (lane + 32 * j) < E ? __float_as_uint(v[j] / sum) + 1u : 0u;
     float wsum = 0.f;
     id_reg = 0;
     w_reg = 0.f;
     for (int k = 0; k < K; ++k) {
-        float best = -INFINITY;
-        int bi = 0x7fffffff;
+        const unsigned int own = max(max(key[0], key[1]), max(key[2], key[3]));
+        const unsigned int top = __reduce_max_sync(0xffffffffu, own);
+        int bi = -1;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (v[j] > best) {
-                best = v[j];
-                bi = lane + 32 * j;
-            }
+        for (int j = 3; j >= 0; --j) {
+            const unsigned int b = __ballot_sync(0xffffffffu, key[j] == top);
+            if (b) bi = 32 * j + __ffs(b) - 1;
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) {
-                best = ob;
-                bi = oi;
-            }
-        }
+        const float best = __uint_as_float(top - 1u);
         wsum += best;
         if (lane == k) {
             id_reg = bi;
@@ -370,37 +428,25 @@ __device__ __forceinline__ void warp_topk(const __half* __restrict__ logits, int
         if ((bi & 31) == lane) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                if (j == (bi >> 5)) v[j] = -1.0e30f;
+                if (j == (bi >> 5)) key[j] = 0u;
         }
     }
     if (norm) w_reg = w_reg / wsum;
     w_reg = __half2float(__float2half_rn(w_reg));  // the routing weights are used in fp16
+    return TopK{id_reg, w_reg};
 }
 
 // ---------------------------------------------------------------------------------------------
-// attention phase (one (head, split) unit per block)
+// attention phase (one (head, split) unit per block): writes the (m, l, acc[D]) partial of its unit
 // ---------------------------------------------------------------------------------------------
 struct AttnScratch {
     float q[128];
-    float tmp[128];
+    float kx[128];
     float red[40];
     float wm[kMegaWarps];
     float wl[kMegaWarps];
     float wacc[kMegaWarps][132];
-    int last;
 };
-
-__device__ __forceinline__ float block_rstd(const __half* __restrict__ row, int A, float eps, float* red) {
-    float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < A; i += blockDim.x * 8) {
-        float f[8];
-        unpack8_h(ld_cg16(row + i), f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
-    }
-    ss = block_sum(ss, red);
-    return 1.0f / sqrtf(ss / static_cast<float>(A) + eps);
-}
 
 template <int D>
 __device__ __forceinline__ __half rope_one(const float* __restrict__ xs, int d, const __half* __restrict__ cos,
@@ -412,7 +458,7 @@ __device__ __forceinline__ __half rope_one(const float* __restrict__ xs, int d, 
 
 template <int D, bool INT8>
 __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLayer& L, AttnScratch& sm) {
-    constexpr int LPP = D / 16;  // lanes per position
+    constexpr int LPP = D / 16;   // lanes per position
     constexpr int GW = 32 / LPP;  // position groups per warp
     const int unit = blockIdx.x;
     if (unit >= p.heads * p.splits) return;
@@ -435,6 +481,7 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
         if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_POSITION);
         pos = pos < 0 ? 0 : p.S - 1;
     }
+    const bool owner = pos_ok && pos >= n_start && pos < n_end;
     const __half* cos = p.rope_cos + pos * D;
     const __half* sin = p.rope_sin + pos * D;
     const int64_t hs = static_cast<int64_t>(p.S) * D;
@@ -445,43 +492,82 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
     __half* kh = L.keys + h * hs;
     __half* vh = L.values + h * hs;
 
-    const float rstd_q = block_rstd(p.qkv, A, p.eps, sm.red);
-    if (tid < D) sm.tmp[tid] = norm_elem(__ldcg(p.qkv + h * D + tid), rstd_q, L.q_norm[h * D + tid]);
+    // sum of squares of the q row (and of the k row for the owner) in one block reduction
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = tid * 8; i < A; i += blockDim.x * 8) {
+        float f[8];
+        unpack8_h(ld_cg16(p.qkv + i), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ssq = fmaf(f[j], f[j], ssq);
+        if (owner) {
+            unpack8_h(ld_cg16(p.qkv + A + i), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ssk = fmaf(f[j], f[j], ssk);
+        }
+    }
+    ssq = warp_sum(ssq);
+    ssk = warp_sum(ssk);
+    if (lane == 0) {
+        sm.red[warp] = ssq;
+        sm.red[kMegaWarps + warp] = ssk;
+    }
     __syncthreads();
-    if (tid < D) sm.q[tid] = __half2float(rope_one<D>(sm.tmp, tid, cos, sin));
+    float tq = 0.f, tk = 0.f;
+    for (int w = 0; w < kMegaWarps; ++w) {
+        tq += sm.red[w];
+        tk += sm.red[kMegaWarps + w];
+    }
+    const float rstd_q = 1.0f / sqrtf(tq / static_cast<float>(A) + p.eps);
+    const float rstd_k = 1.0f / sqrtf(tk / static_cast<float>(A) + p.eps);
+    if (tid < D) {
+        sm.q[tid] = norm_elem(__ldcg(p.qkv + h * D + tid), rstd_q, L.q_norm[h * D + tid]);
+        if (owner) sm.kx[tid] = norm_elem(__ldcg(p.qkv + A + h * D + tid), rstd_k, L.k_norm[h * D + tid]);
+    }
     __syncthreads();
-    const bool owner = pos_ok && pos >= n_start && pos < n_end;
-    if (owner) {
-        const float rstd_k = block_rstd(p.qkv + A, A, p.eps, sm.red);
-        if (tid < D) sm.tmp[tid] = norm_elem(__ldcg(p.qkv + A + h * D + tid), rstd_k, L.k_norm[h * D + tid]);
-        __syncthreads();
-        __half kn = __float2half_rn(0.f), vn = __float2half_rn(0.f);
-        if (tid < D) {
-            kn = rope_one<D>(sm.tmp, tid, cos, sin);
+    float qd = 0.f;
+    __half kn = __float2half_rn(0.f), vn = __float2half_rn(0.f);
+    if (tid < D) {
+        qd = __half2float(rope_one<D>(sm.q, tid, cos, sin));
+        if (owner) {
+            kn = rope_one<D>(sm.kx, tid, cos, sin);
             vn = __ldcg(p.qkv + 2 * A + h * D + tid);
             kh[pos * D + tid] = kn;
             vh[pos * D + tid] = vn;
         }
-        if (INT8) {
-            const float kf = __half2float(kn), vf = __half2float(vn);
-            const float amk = block_max(tid < D ? fabsf(kf) : 0.f, sm.red);
-            const float amv = block_max(tid < D ? fabsf(vf) : 0.f, sm.red);
-            const float sk = amk > 0.f ? __fdiv_rn(amk, 127.0f) : 1.0f;
-            const float sv = amv > 0.f ? __fdiv_rn(amv, 127.0f) : 1.0f;
-            if (tid < D) {
-                float qk = fminf(fmaxf(rintf(__fdiv_rn(kf, sk)), -127.0f), 127.0f);
-                float qv = fminf(fmaxf(rintf(__fdiv_rn(vf, sv)), -127.0f), 127.0f);
-                kc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qk));
-                vc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qv));
-            }
-            if (tid == 0) {
-                ks[pos] = __float2half_rn(sk);
-                vs[pos] = __float2half_rn(sv);
-            }
-        }
-        __threadfence_block();
-        __syncthreads();
     }
+    float amk = 0.f, amv = 0.f;
+    if (owner && INT8) {
+        amk = warp_max(tid < D ? fabsf(__half2float(kn)) : 0.f);
+        amv = warp_max(tid < D ? fabsf(__half2float(vn)) : 0.f);
+        if (lane == 0 && warp < (D + 31) / 32) {
+            sm.wm[warp] = amk;
+            sm.wl[warp] = amv;
+        }
+    }
+    __syncthreads();  // everyone has read sm.q (un-rotated) and the owner's partial maxima are in place
+    if (tid < D) sm.q[tid] = qd;
+    if (owner && INT8) {
+        amk = 0.f;
+        amv = 0.f;
+        for (int w = 0; w < (D + 31) / 32; ++w) {
+            amk = fmaxf(amk, sm.wm[w]);
+            amv = fmaxf(amv, sm.wl[w]);
+        }
+        const float sk = amk > 0.f ? __fdiv_rn(amk, 127.0f) : 1.0f;
+        const float sv = amv > 0.f ? __fdiv_rn(amv, 127.0f) : 1.0f;
+        if (tid < D) {
+            const float qk = fminf(fmaxf(rintf(__fdiv_rn(__half2float(kn), sk)), -127.0f), 127.0f);
+            const float qv = fminf(fmaxf(rintf(__fdiv_rn(__half2float(vn), sv)), -127.0f), 127.0f);
+            kc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qk));
+            vc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qv));
+        }
+        if (tid == 0) {
+            ks[pos] = __float2half_rn(sk);
+            vs[pos] = __float2half_rn(sv);
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
 
     float q[16];
 #pragma unroll
@@ -586,7 +672,9 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
         }
     }
     __syncthreads();
-    float* part = p.attn_part + (static_cast<int64_t>(h) * p.splits + split) * (D + 2);
+    // partial layout: acc[(h*S + split)*D + d], then the (m, l) pairs
+    float* part = p.attn_part + (static_cast<int64_t>(h) * p.splits + split) * D;
+    float* part_ml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + (static_cast<int64_t>(h) * p.splits + split) * 2;
     if (tid < D) {
         float big = -INFINITY;
         for (int w = 0; w < kMegaWarps; ++w) big = fmaxf(big, sm.wm[w]);
@@ -597,67 +685,196 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
             a = fmaf(sm.wacc[w][tid], wt, a);
             l = fmaf(sm.wl[w], wt, l);
         }
-        part[2 + tid] = a;
+        part[tid] = a;
         if (tid == 0) {
-            part[0] = big;
-            part[1] = l;
+            part_ml[0] = big;
+            part_ml[1] = l;
         }
     }
+    // The block that arrives last at its head's counter merges the splits of the head: every block then
+    // reads the finished 2*D bytes per head instead of all partials.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned int ticket = atomicAdd(p.attn_counters + h, 1u);
-        sm.last = (ticket == static_cast<unsigned int>(p.splits) - 1u);
+        const unsigned int prev = atomicAdd(p.attn_counters + h, 1u);
+        const bool is_last = prev + 1u == static_cast<unsigned int>(p.splits);
+        if (is_last) p.attn_counters[h] = 0u;  // everyone of this layer has arrived: ready for the next one
+        sm.red[0] = is_last ? 1.f : 0.f;
     }
     __syncthreads();
-    if (!sm.last) return;
-    __threadfence();
-    if (tid < D) {
-        const float* hp = p.attn_part + static_cast<int64_t>(h) * p.splits * (D + 2);
+    if (sm.red[0] != 0.f && tid < D) {
+        __threadfence();
+        const float* hacc = p.attn_part + static_cast<int64_t>(h) * p.splits * D + tid;
+        const float* hml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + static_cast<int64_t>(h) * p.splits * 2;
+        float av[kMaxSplits];
+        float2 mv[kMaxSplits];
+#pragma unroll
+        for (int j = 0; j < kMaxSplits; ++j) {
+            if (j < p.splits) {
+                av[j] = __ldcg(hacc + j * D);
+                mv[j] = __ldcg(reinterpret_cast<const float2*>(hml + 2 * j));
+            }
+        }
         float big = -INFINITY;
-        for (int j = 0; j < p.splits; ++j) big = fmaxf(big, __ldcg(hp + j * (D + 2)));
+#pragma unroll
+        for (int j = 0; j < kMaxSplits; ++j)
+            if (j < p.splits) big = fmaxf(big, mv[j].x);
         big = big > -INFINITY ? big : 0.f;
         float num = 0.f, den = 0.f;
-        for (int j = 0; j < p.splits; ++j) {
-            const float w = exp2f(__ldcg(hp + j * (D + 2)) - big);
-            num = fmaf(__ldcg(hp + j * (D + 2) + 2 + tid), w, num);
-            den = fmaf(__ldcg(hp + j * (D + 2) + 1), w, den);
+#pragma unroll
+        for (int j = 0; j < kMaxSplits; ++j) {
+            if (j < p.splits) {
+                const float w = exp2f(mv[j].x - big);
+                den = fmaf(mv[j].y, w, den);
+                num = fmaf(av[j], w, num);
+            }
         }
         p.attn[h * D + tid] = __float2half_rn(den > 0.f ? num / den : num);
     }
-    if (tid == 0) p.attn_counters[h] = 0u;
 }
 
-// Phase time stamps (block 0, thread 0; nanoseconds of the global timer) for profiling the step.
-__device__ __forceinline__ void stamp(const MegaParams& p, int slot) {
-    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        p.stamps[slot] = t;
+// ---------------------------------------------------------------------------------------------
+// block-wide preparation of a phase's activation vector
+// ---------------------------------------------------------------------------------------------
+// Sum over the block with ONE barrier: every thread adds the per-warp partials in warp order.
+// `red` (>= kMegaWarps floats) must not be reused before the next block barrier.
+__device__ __forceinline__ float block_sum_once(float v, float* red) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMegaWarps; ++w) t += red[w];
+    return t;
+}
+
+constexpr int kPrepItems = 2;  // 4-element items per thread: covers vectors up to 8 * kMegaThreads wide
+
+// RMSNorm(row) * nw (just row when nw is null) -> digit planes at dst (and, when f32out is given, the fp32 values in the lane-major
+// layout ((c*4 + q)*32 + ln)*4 + r for k = c*512 + ln*16 + q*4 + r).  One global round trip: the raw
+// values stay in registers between the statistic and the normalisation.
+__device__ __noinline__ void prepare_norm(const MegaParams& p, int dbg, uint32_t* dst, float* red, const __half* __restrict__ row,
+                                             const __half* __restrict__ nw, int n, float eps, float* f32out) {
+    dbg_clock(p, dbg + 0);
+    uint2 xv[kPrepItems], wv[kPrepItems];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kPrepItems; ++it) {
+        const int item = threadIdx.x + it * kMegaThreads;
+        xv[it] = make_uint2(0u, 0u);
+        wv[it] = make_uint2(0u, 0u);
+        if (item < n / 4) {
+            xv[it] = __ldcg(reinterpret_cast<const uint2*>(row + 4 * item));
+            if (nw != nullptr) wv[it] = *reinterpret_cast<const uint2*>(nw + 4 * item);
+        }
+        const __half* xh = reinterpret_cast<const __half*>(&xv[it]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f = __half2float(xh[j]);
+            ss = fmaf(f, f, ss);
+        }
     }
+    dbg_clock(p, dbg + 1);
+    const float rstd = nw != nullptr ? 1.0f / sqrtf(block_sum_once(ss, red) / static_cast<float>(n) + eps) : 0.f;
+    dbg_clock(p, dbg + 2);
+#pragma unroll
+    for (int it = 0; it < kPrepItems; ++it) {
+        const int item = threadIdx.x + it * kMegaThreads;
+        if (item - (threadIdx.x & 31) < n / 4) {  // whole warps take part in the shuffles
+            const __half* xh = reinterpret_cast<const __half*>(&xv[it]);
+            const __half* wh = reinterpret_cast<const __half*>(&wv[it]);
+            float f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = nw != nullptr ? norm_elem(xh[j], rstd, wh[j]) : __half2float(xh[j]);
+            const bool on = item < n / 4;
+            quantise_item(dst, n / 16, item, on, f);
+            if (f32out != nullptr && on) {
+                const int k = 4 * item;
+                const int c = k >> 9, ln = (k & 511) >> 4, q = (k & 15) >> 2;
+                *reinterpret_cast<float4*>(f32out + (((c * 4 + q) * 32 + ln) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
+            }
+        }
+    }
+    dbg_clock(p, dbg + 3);
+    __syncthreads();
+    dbg_clock(p, dbg + 4);
+}
+
+// The K expert activation vectors (fp16, K x F) -> digit planes, vector `slot` at dst + slot * vec_words.
+__device__ __noinline__ void prepare_act(uint32_t* dst, const MegaParams& p, int vec_words) {
+    const int per = p.F / 4, total = p.K * per;  // items per vector / in all
+    for (int base = 0; base < total; base += 4 * kMegaThreads) {
+        uint2 xv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int item = base + u * kMegaThreads + threadIdx.x;
+            xv[u] = make_uint2(0u, 0u);
+            if (item < total) xv[u] = __ldcg(reinterpret_cast<const uint2*>(p.act + 4 * static_cast<int64_t>(item)));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int item = base + u * kMegaThreads + threadIdx.x;
+            if (item - (threadIdx.x & 31) < total) {
+                const bool on = item < total;
+                const int slot = on ? item / per : 0;
+                const int within = item - slot * per;
+                const __half* xh = reinterpret_cast<const __half*>(&xv[u]);
+                float f[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) f[j] = __half2float(xh[j]);
+                quantise_item(dst + slot * vec_words, p.F / 16, within, on, f);
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// L2 prefetch of a byte range by the whole block (128-byte lines).
+__device__ __forceinline__ void prefetch_l2(const void* ptr, int64_t bytes) {
+    const char* c = reinterpret_cast<const char*>(ptr);
+    for (int64_t off = static_cast<int64_t>(threadIdx.x) * 128; off < bytes; off += static_cast<int64_t>(kMegaThreads) * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
 }
 
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
+// One loop over the 6*layers + 1 phases with one task loop inside: the instruction footprint of a
+// layer stays small enough to live in the instruction cache (every phase runs once per layer, so
+// straight-line per-phase code would be fetched from L2 again in every layer).
 __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid_constant__ MegaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* scratch = smem + kMegaWarps * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 128;
     scratch = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(scratch) + 127) & ~uintptr_t(127));
+    uint32_t* xq_s = reinterpret_cast<uint32_t*>(scratch);  // quantised activation vector (<= 6.7 KB)
+    float* red = reinterpret_cast<float*>(scratch + 7168);   // reduction scratch
+    float* h2f = reinterpret_cast<float*>(scratch + 7680);   // fp32 h2, lane-major, for the fp16 router rows (8 KB)
+    StreamTable& table = *reinterpret_cast<StreamTable*>(scratch + kMegaScratchBytes);
 
     WarpStream ws;
     ws.P = &p;
-    ws.ring.init(smem, warp, kMegaWarps, kMegaStageBytes, lane);
-    ws.my = smem + static_cast<size_t>(warp) * kMegaStages * kMegaStageBytes;
+    ws.T = &table;
     ws.G = gridDim.x * kMegaWarps;
     ws.wg = warp * gridDim.x + blockIdx.x;
     ws.lane = lane;
-    ws.n_issued = ws.n_consumed = 0;
+    ws.cnt[KIND_A] = ws.count(3 * p.heads * p.D / 2);
+    ws.cnt[KIND_C] = ws.count(p.H / 2);
+    ws.cnt[KIND_D] = ws.count(p.E);
+    ws.cnt[KIND_E] = ws.count(p.K * p.F);
+    ws.cnt[KIND_F] = ws.count(p.H);
+    ws.cnt_lm = ws.count(p.V / 2);
+    ws.sps = min(min(4, p.K), kMegaStageBytes / (p.F + 2 * (p.F / p.group)));
+    if (threadIdx.x == 0) build_stream_table(table, p, ws.sps);
+    ws.ring.init(smem, warp, kMegaWarps, kMegaStageBytes, lane);
+    ws.my = smem + static_cast<size_t>(warp) * kMegaStages * kMegaStageBytes;
+    ws.inflight = 0;
+    ws.depth = min(max(p.depth, 1), kMegaStages);
+    ws.i_stage = ws.c_stage = ws.c_par = 0;
     ws.ids_ready_layer = -1;
     ws.ids_reg = 0;
-    ws.cur = Cursor{0, PH_A, 0, 0};
-    ws.normalise();
+    __syncthreads();
+    ws.start();
     ws.pump();
 
     GridBarrier bar;
@@ -667,195 +884,159 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 
     stamp(p, 0);
     const int A = p.heads * p.D;
-    LaneLite ll;
-    ll.lane16 = lane * 16;
-    ll.sbase = (lane * 16) / p.group;
-    ll.sstride = 512 / p.group;
-    const int gH = p.H / p.group, gA = A / p.group, gF = p.F / p.group;
+    const int lane16 = lane * 16;
+    const int sbase = lane16 / p.group, sstride = 512 / p.group;
+    const int vec_words = 3 * (p.F / 16) * 4 + p.F / 16;  // one quantised expert activation vector
+
+    // This block's slice of the KV cache is the same in every layer: prefetch it into L2 one phase ahead.
+    int kv_first = 0, kv_count = 0;
+    if (static_cast<int>(blockIdx.x) < p.heads * p.splits) {
+        int nf = *p.filled;
+        nf = nf < 0 ? 0 : (nf > p.S ? p.S : nf);
+        const int h = blockIdx.x / p.splits, split = blockIdx.x - h * p.splits;
+        const int chunk = (nf + p.splits - 1) / p.splits;
+        const int n0 = split * chunk, n1 = min(n0 + chunk, nf);
+        kv_first = h * p.S + n0;
+        kv_count = n1 > n0 ? n1 - n0 : 0;
+    }
 
     const __half* x_prev = p.embed + (*p.token) * static_cast<int64_t>(p.H);
-    XSlice<NCH, kMegaMode> xs;
+    float tw_reg = 0.f;
+    int l = 0, ph = 0;  // phase: 0 q.k.v / lm_head, 1 attention, 2 o_proj, 3 router, 4 gate/up, 5 down
+    const int nphases = 6 * p.layers + 1;
 
-    for (int l = 0; l < p.layers; ++l) {
+#pragma unroll 1
+    for (int step = 0; step < nphases; ++step) {
         const MegaLayer& L = p.L[l];
-        // ---- A: q.k.v -------------------------------------------------------------------------------
-        {
-            const int cnt = ws.phase_count(PH_A);
-            if (cnt > 0) slice_norm(xs, x_prev, L.ln1, p.eps, p.H, ll.lane16);
-            for (int i = 0; i < cnt; ++i) {
-                const unsigned char* st = ws.acquire();
-                if (!st) break;
-                const __half* sc = reinterpret_cast<const __half*>(st + 2 * p.H);
-                float a0 = row_dot(st, sc, p.H, ll, xs);
-                float a1 = row_dot(st + p.H, sc + gH, p.H, ll, xs);
-                ws.release();
-                a0 = warp_sum(a0);
-                a1 = warp_sum(a1);
-                if (lane < 2) p.qkv[(ws.wg + i * ws.G) * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
+        const bool last = l == p.layers;
+        int ntasks = 0, K = p.H, nst = 1;
+        if (ph == 0) dbg_clock(p, 24);
+        if (ph == 2) dbg_clock(p, 25);
+        // ---- block-wide preparation of the phase -----------------------------------------------------
+        if (ph == 0 || ph == 2 || ph == 3) {
+            if (ph == 0 && !last && kv_count > 0) {
+                const int64_t eb = p.kv_int8 ? 1 : 2;
+                const void* kp = p.kv_int8 ? static_cast<const void*>(L.kc + static_cast<int64_t>(kv_first) * p.D)
+                                           : static_cast<const void*>(L.keys + static_cast<int64_t>(kv_first) * p.D);
+                const void* vp = p.kv_int8 ? static_cast<const void*>(L.vc + static_cast<int64_t>(kv_first) * p.D)
+                                           : static_cast<const void*>(L.values + static_cast<int64_t>(kv_first) * p.D);
+                prefetch_l2(kp, static_cast<int64_t>(kv_count) * p.D * eb);
+                prefetch_l2(vp, static_cast<int64_t>(kv_count) * p.D * eb);
+                if (p.kv_int8) {
+                    prefetch_l2(L.ks + kv_first, static_cast<int64_t>(kv_count) * 2);
+                    prefetch_l2(L.vs + kv_first, static_cast<int64_t>(kv_count) * 2);
+                }
             }
-        }
-        bar.sync();
-        stamp(p, 6 * l + 1);
-        // ---- B: attention ---------------------------------------------------------------------------
-        {
+            if (ph == 0) dbg_clock(p, 26);
+            if (ph == 2) K = A;
+            prepare_norm(p, ph == 0 ? 0 : 8, xq_s, red, ph == 0 ? x_prev : (ph == 2 ? p.attn : p.xa),
+                         ph == 0 ? L.ln1 : (ph == 2 ? nullptr : L.ln2), K, p.eps, ph == 3 ? h2f : nullptr);
+            ntasks = ph == 0 ? (last ? ws.cnt_lm : ws.cnt[KIND_A]) : (ph == 2 ? ws.cnt[KIND_C] : ws.cnt[KIND_D]);
+        } else if (ph == 1) {
             AttnScratch& sm = *reinterpret_cast<AttnScratch*>(scratch);
-            if (p.D == 128) {
-                if (p.kv_int8) attention_phase<128, true>(p, L, sm);
-                else attention_phase<128, false>(p, L, sm);
-            } else {
-                if (p.kv_int8) attention_phase<64, true>(p, L, sm);
-                else attention_phase<64, false>(p, L, sm);
-            }
-        }
-        bar.sync();
-        stamp(p, 6 * l + 2);
-        // ---- C: o_proj + residual -------------------------------------------------------------------
-        {
-            const int cnt = ws.phase_count(PH_C);
-            if (cnt > 0) slice_plain(xs, p.attn, A, ll.lane16);
-            for (int i = 0; i < cnt; ++i) {
-                const unsigned char* st = ws.acquire();
-                if (!st) break;
-                const __half* sc = reinterpret_cast<const __half*>(st + 2 * A);
-                float a0 = row_dot(st, sc, A, ll, xs);
-                float a1 = row_dot(st + A, sc + gA, A, ll, xs);
-                ws.release();
-                a0 = warp_sum(a0);
-                a1 = warp_sum(a1);
-                if (lane < 2) {
-                    const int n = (ws.wg + i * ws.G) * 2 + lane;
-                    p.xa[n] = __hadd(__float2half_rn(lane == 0 ? a0 : a1), __ldcg(x_prev + n));
-                }
-            }
-        }
-        bar.sync();
-        stamp(p, 6 * l + 3);
-        // ---- D: router logits -----------------------------------------------------------------------
-        {
-            const int cnt = ws.phase_count(PH_D);
-            RawRow rr;
-            if (cnt > 0) rr.load(p.xa, p.H, ll.lane16, p.eps);
-            for (int i = 0; i < cnt; ++i) {
-                const unsigned char* st = ws.acquire();
-                if (!st) break;
-                float a = 0.f;
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    const int k0 = c * 512 + ll.lane16;
-                    if (k0 < p.H) {
-                        float hf[16];
-                        rr.chunk(c, L.ln2, p.H, ll.lane16, hf);
-                        const uint4 w0 = *reinterpret_cast<const uint4*>(st + 2 * k0);
-                        const uint4 w1 = *reinterpret_cast<const uint4*>(st + 2 * k0 + 16);
-                        a += dot8_h(w0, &hf[0]);
-                        a += dot8_h(w1, &hf[8]);
-                    }
-                }
-                ws.release();
-                a = warp_sum(a);
-                if (lane == 0) p.router_logits[static_cast<int64_t>(l) * p.E + ws.wg + i * ws.G] = __float2half_rn(a);
-            }
-        }
-        bar.sync();
-        stamp(p, 6 * l + 4);
-        // ---- E: routing (per warp) + expert gate/up ----------------------------------------------------
-        float tw_reg;
-        {
-            warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane, ws.ids_reg, tw_reg);
+            if (p.kv_int8) attention_phase<128, true>(p, L, sm);
+            else attention_phase<128, false>(p, L, sm);
+        } else if (ph == 4) {
+            const TopK tk = warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane);
+            ws.ids_reg = tk.id;
+            tw_reg = tk.w;
             ws.ids_ready_layer = l;
             ws.pump();
             if (blockIdx.x == 0 && warp == 0 && lane < p.K) {
                 p.top_i[static_cast<int64_t>(l) * p.K + lane] = ws.ids_reg;
                 p.top_w[lane] = __float2half_rn(tw_reg);
             }
-            const int cnt = ws.phase_count(PH_E);
-            if (cnt > 0) slice_norm(xs, p.xa, L.ln2, p.eps, p.H, ll.lane16);
-            for (int i = 0; i < cnt; ++i) {
-                const unsigned char* st = ws.acquire();
-                if (!st) break;
-                const __half* sc = reinterpret_cast<const __half*>(st + 2 * p.H);
-                float g = row_dot(st, sc, p.H, ll, xs);
-                float u = row_dot(st + p.H, sc + gH, p.H, ll, xs);
-                ws.release();
-                g = warp_sum(g);
-                u = warp_sum(u);
-                if (lane == 0) p.act[ws.wg + i * ws.G] = __float2half_rn(g * (1.0f / (1.0f + expf(-g))) * u);
-            }
+            ntasks = ws.cnt[KIND_E];
+        } else {
+            prepare_act(reinterpret_cast<uint32_t*>(scratch), p, vec_words);
+            K = p.F;
+            ntasks = ws.cnt[KIND_F];
+            nst = (p.K + ws.sps - 1) / ws.sps;
         }
-        bar.sync();
-        stamp(p, 6 * l + 5);
-        // ---- F: expert down + residual ----------------------------------------------------------------
-        {
-            // stage the K activation vectors as packed fp16, lane-major
-            const int per_slot = p.F / 8;
-            const int nchF = (p.F + 511) / 512;
-            for (int idx = threadIdx.x; idx < p.K * per_slot; idx += blockDim.x) {
-                const int slot = idx / per_slot;
-                const int k = (idx - slot * per_slot) * 8;
-                const uint4 raw = ld_cg16(p.act + static_cast<int64_t>(slot) * p.F + k);
-                const int c = k >> 9, ln = (k & 511) >> 4, hi = (k >> 3) & 1;
-                *reinterpret_cast<uint4*>(scratch + (static_cast<size_t>((slot * nchF + c) * 32 + ln) * 16 + hi * 8) * 2) = raw;
-            }
-            __syncthreads();
-            const int cnt = ws.phase_count(PH_F);
-            for (int i = 0; i < cnt; ++i) {
-                float acc0 = 0.f, acc1 = 0.f;
-                bool dead = false;
-                for (int slot = 0; slot < p.K; ++slot) {
-                    const unsigned char* st = ws.acquire();
-                    if (!st) {
-                        dead = true;
-                        break;
-                    }
-                    const __half* sc = reinterpret_cast<const __half*>(st + 2 * p.F);
+        substamp(p, l, 2 * ph);
+        const int gK = K / p.group;
+
+        // ---- this warp's tasks of the phase ---------------------------------------------------------------
+#pragma unroll 1
+        for (int i = 0; i < ntasks; ++i) {
+            const int task = ws.wg + i * ws.G;
+            float a0 = 0.f, a1 = 0.f;
+            bool dead = false;
+#pragma unroll 1
+            for (int s = 0; s < nst; ++s) {
+                const unsigned char* st = ws.acquire();
+                if (!st) {
+                    dead = true;
+                    break;
+                }
+                if (ph == 3) {  // one fp16 router row against the fp32 h2
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
-                        if (c * 512 + ll.lane16 < p.F) {
-                            const unsigned char* src = scratch + static_cast<size_t>((slot * nchF + c) * 32 + lane) * 32;
-                            float f[16];
-                            unpack8_h(*reinterpret_cast<const uint4*>(src), &f[0]);
-                            unpack8_h(*reinterpret_cast<const uint4*>(src + 16), &f[8]);
-                            xs.set(c, f);
+                        const int k0 = c * 512 + lane16;
+                        if (k0 < p.H) {
+                            float hf[16];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float4 v = *reinterpret_cast<const float4*>(h2f + (((c * 4 + q) * 32 + lane) << 2));
+                                hf[4 * q] = v.x;
+                                hf[4 * q + 1] = v.y;
+                                hf[4 * q + 2] = v.z;
+                                hf[4 * q + 3] = v.w;
+                            }
+                            a0 += dot8_h(*reinterpret_cast<const uint4*>(st + 2 * k0), &hf[0]);
+                            a0 += dot8_h(*reinterpret_cast<const uint4*>(st + 2 * k0 + 16), &hf[8]);
                         }
                     }
-                    const float p0 = row_dot(st, sc, p.F, ll, xs);
-                    const float p1 = row_dot(st + p.F, sc + gF, p.F, ll, xs);
-                    ws.release();
-                    const float tw = __shfl_sync(0xffffffffu, tw_reg, slot);
-                    acc0 = fmaf(tw, p0, acc0);
-                    acc1 = fmaf(tw, p1, acc1);
+                } else if (ph == 5) {  // down row n of up to sps routed experts
+                    const int slot0 = s * ws.sps;
+                    const int nsl = min(ws.sps, p.K - slot0);
+#pragma unroll 1
+                    for (int j = 0; j < nsl; ++j) {
+                        const unsigned char* const rows[1] = {st + j * p.F};
+                        const __half* const scs[1] = {reinterpret_cast<const __half*>(st + ws.sps * p.F) + j * gK};
+                        float part[1];
+                        dp_rows<1>(part, rows, scs, reinterpret_cast<const uint32_t*>(scratch) + (slot0 + j) * vec_words, p.F, lane,
+                                   sbase, sstride);
+                        a0 = fmaf(__shfl_sync(0xffffffffu, tw_reg, slot0 + j), part[0], a0);
+                    }
+                } else {  // two W8 rows of width K
+                    const __half* sc = reinterpret_cast<const __half*>(st + 2 * K);
+                    const unsigned char* const rows[2] = {st, st + K};
+                    const __half* const scs[2] = {sc, sc + gK};
+                    float part[2];
+                    dp_rows<2>(part, rows, scs, xq_s, K, lane, sbase, sstride);
+                    a0 = part[0];
+                    a1 = part[1];
                 }
-                if (dead) break;
-                acc0 = warp_sum(acc0);
-                acc1 = warp_sum(acc1);
-                if (lane < 2) {
-                    const int n = (ws.wg + i * ws.G) * 2 + lane;
-                    p.xb[n] = __hadd(__float2half_rn(lane == 0 ? acc0 : acc1), __ldcg(p.xa + n));
-                }
+                ws.release();
             }
-        }
-        bar.sync();
-        stamp(p, 6 * l + 6);
-        x_prev = p.xb;
-    }
-    // ---- lm_head ------------------------------------------------------------------------------------------
-    {
-        const int cnt = ws.phase_count(PH_LM);
-        if (cnt > 0) slice_norm(xs, x_prev, p.final_norm, p.eps, p.H, ll.lane16);
-        for (int i = 0; i < cnt; ++i) {
-            const unsigned char* st = ws.acquire();
-            if (!st) break;
-            const __half* sc = reinterpret_cast<const __half*>(st + 2 * p.H);
-            float a0 = row_dot(st, sc, p.H, ll, xs);
-            float a1 = row_dot(st + p.H, sc + gH, p.H, ll, xs);
-            ws.release();
+            if (dead) break;
             a0 = warp_sum(a0);
             a1 = warp_sum(a1);
-            if (lane < 2) p.logits[(ws.wg + i * ws.G) * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
+            if (ph == 0) {
+                if (lane < 2) (last ? p.logits : p.qkv)[task * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
+            } else if (ph == 2) {
+                if (lane < 2) {
+                    const int n = task * 2 + lane;
+                    p.xa[n] = __hadd(__float2half_rn(lane == 0 ? a0 : a1), __ldcg(x_prev + n));
+                }
+            } else if (ph == 3) {
+                if (lane == 0) p.router_logits[static_cast<int64_t>(l) * p.E + task] = __float2half_rn(a0);
+            } else if (ph == 4) {
+                if (lane == 0) p.act[task] = __float2half_rn(a0 * (1.0f / (1.0f + expf(-a0))) * a1);
+            } else {
+                if (lane == 0) p.xb[task] = __hadd(__float2half_rn(a0), __ldcg(p.xa + task));
+            }
+        }
+        substamp(p, l, 2 * ph + 1);
+        bar.sync();
+        stamp(p, step + 1);
+        if (++ph == 6) {
+            ph = 0;
+            ++l;
+            x_prev = p.xb;
         }
     }
-    bar.sync();
-    stamp(p, 6 * p.layers + 1);
     if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(p.bar_epoch, 1u);
 }
 
@@ -863,8 +1044,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 // host side
 // ---------------------------------------------------------------------------------------------
 size_t mega_smem_bytes() {
-    return static_cast<size_t>(kMegaWarps) * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 256 +
-           kMegaScratchBytes;
+    return static_cast<size_t>(kMegaWarps) * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 512 +
+           kMegaScratchBytes + sizeof(StreamTable);
 }
 
 bool mega_eligible(const lemoq_step_desc& d) {
@@ -873,32 +1054,39 @@ bool mega_eligible(const lemoq_step_desc& d) {
     if (g <= 0 || g % 16 != 0 || 512 % g != 0) return false;
     auto ok_dim = [&](int n) { return n % 512 == 0 && n <= 2048 && n % g == 0 && ((n / g) * 2 * 2) % 16 == 0; };
     if (!ok_dim(d.hidden) || !ok_dim(A) || !ok_dim(d.ffn)) return false;
-    if (((d.hidden / g) * 2) % 16 != 0) return false;  // one expert row of scales must be a 16-byte multiple
-    if (d.head_dim != 64 && d.head_dim != 128) return false;
+    // one expert row of scales (gate/up rows and down rows are copied singly) must be a 16-byte multiple
+    if (((d.hidden / g) * 2) % 16 != 0 || ((d.ffn / g) * 2) % 16 != 0) return false;
+    if (d.ffn + 2 * (d.ffn / g) > kMegaStageBytes) return false;
+    if (d.head_dim != 128) return false;
     if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
     if (d.vocab % 2 != 0) return false;
-    if (static_cast<size_t>(d.top_k) * ((d.ffn + 511) / 512) * 512 * 2 > kMegaScratchBytes) return false;
+    const size_t vec_words = 3 * (d.ffn / 16) * 4 + d.ffn / 16;
+    if (static_cast<size_t>(d.top_k) * vec_words * 4 > kMegaScratchBytes) return false;
     if (sizeof(AttnScratch) > kMegaScratchBytes) return false;
     return true;
 }
 
 int mega_grid(const lemoq_step_desc& d, int splits) {
-    int dev = 0, sms = 0, per_sm = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    if (cudaFuncSetAttribute(step_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(mega_smem_bytes())) != cudaSuccess)
-        return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, step_mega_kernel, kMegaThreads, mega_smem_bytes()) !=
-            cudaSuccess ||
-        per_sm < 1)
-        return 0;
-    int coop = 0;
-    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
-    if (!coop) return 0;
     (void)d;
     (void)splits;
-    return sms;
+    const bool verbose = getenv("LEMOQ_VERBOSE") != nullptr;
+    int dev = 0, sms = 0, per_sm = 0, coop = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(step_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(mega_smem_bytes()));
+    if (err == cudaSuccess)
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, step_mega_kernel, kMegaThreads, mega_smem_bytes());
+    if (verbose)
+        fprintf(stderr, "lemoq: whole-step kernel: %s, sms %d, cooperative %d, blocks/SM %d, smem %zu\n",
+                cudaGetErrorString(err), sms, coop, per_sm, mega_smem_bytes());
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return (coop && per_sm >= 1) ? sms : 0;
 }
 
 int launch_step_mega(const MegaParams& p, int grid, cudaStream_t stream) {

@@ -22,6 +22,7 @@ int g_stream_warps = 16;
 int g_dot_mode = DOT_F16_FOLD;
 extern int g_step_skip_mask;
 extern int g_step_use_mega;
+extern int g_mega_depth;
 int g_debug_skip_scale_copy = 0;  // timing experiments only: results are wrong when set
 
 // ---------------------------------------------------------------------------
@@ -371,6 +372,10 @@ int set_stream_tuning(int key, int value) {
     }
     if (key == 4) {
         g_step_use_mega = value;
+        return LEMOQ_OK;
+    }
+    if (key == 5 && value >= 1 && value <= 8) {
+        g_mega_depth = value;
         return LEMOQ_OK;
     }
     return set_error(LEMOQ_ERR_INVALID, "set_tuning: unknown key %d or value %d out of range", key, value);

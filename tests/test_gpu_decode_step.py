@@ -146,7 +146,25 @@ def test_small_model_fp16_kv_arm(monkeypatch):
     session.close()
 
 
+@pytest.fixture
+def whole_step_kernel():
+    """Run the step engine as the single cooperative kernel (opt-in tuning key 4) for one test."""
+    from lemoq import _cabi
+
+    _cabi.call("lemoq_set_tuning", 4, 1)
+    yield
+    _cabi.call("lemoq_set_tuning", 4, 0)
+
+
+def test_one_full_size_layer_whole_step_kernel(whole_step_kernel):
+    _one_full_size_layer(expect_kernels=1)
+
+
 def test_one_full_size_layer_at_ctx_1024():
+    _one_full_size_layer(expect_kernels=None)
+
+
+def _one_full_size_layer(expect_kernels):
     """One OLMoE-sized decoder layer (hidden 2048, 16x128 heads, 64 experts top-8, ffn 1024) decoding at
     position 1024 over a seeded N(0,1) fp16 KV cache, input hidden N(0,1): logits, expert ids, KV codes."""
     from benchmarks.cudagraph import StaticCacheDecodeSession
@@ -176,6 +194,8 @@ def test_one_full_size_layer_at_ctx_1024():
         if engine == "step":
             ids = session.step_topk_ids()[0].cpu().tolist()
             assert session.step_error_flags() == 0
+            if expect_kernels is not None:
+                assert session.capture_info["kernels_per_step"] == expect_kernels
         bufs = model.model.layers[0].self_attn._lemoq_kv_int8_bufs
         kc_new, ks_new = bufs["kc"][0, :, ctx].cpu(), bufs["ks"][0, :, ctx].cpu()
         k_new = session.cache.layers[0].keys[0, :, ctx].cpu()
@@ -192,8 +212,16 @@ def test_one_full_size_layer_at_ctx_1024():
     assert rel_err(k_new, st.keys[0][0, :, ctx]) < PER_KERNEL_REL_TOL
 
 
+def test_full_model_whole_step_kernel(whole_step_kernel):
+    _full_model_greedy(1024, expect_kernels=1)
+
+
 @pytest.mark.parametrize("ctx", [1024])
 def test_full_model_32_greedy_steps_vs_oracle(ctx):
+    _full_model_greedy(ctx, expect_kernels=None)
+
+
+def _full_model_greedy(ctx, expect_kernels):
     """The canonical cell at full size: 16 layers, vocab 50304, all-ones prompt prefilled on the GPU,
     then 32 greedy steps through the captured graph; the oracle decodes on the CPU from a copy of the
     same prefilled cache with the same quantised weights."""
@@ -207,6 +235,8 @@ def test_full_model_32_greedy_steps_vs_oracle(ctx):
     prompt = torch.full((1, ctx), 1, dtype=torch.long, device=DEV)
     session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=steps, engine="step")
     session.capture(warmup=3)
+    if expect_kernels is not None:
+        assert session.capture_info["kernels_per_step"] == expect_kernels
     session.reset()
     first = session.seed_token_id
     wq = oracle_weights_from_model(model, spec)
