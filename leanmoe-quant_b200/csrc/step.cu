@@ -96,7 +96,7 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * (d.layers + 1));
-    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 64));
+    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 128));
 #undef LEMOQ_TAKE
     return c.off;
 }
@@ -125,6 +125,7 @@ static int validate(const lemoq_step_desc& d) {
 
 namespace lemoq {
 int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
+int g_mega_debug = 0;      // lemoq_set_tuning key 6: timing experiments of the whole-step kernel (wrong results)
 int g_mega_depth = 8;      // lemoq_set_tuning key 5: stages a warp of the whole-step kernel keeps in flight (capped by its ring)
 int g_step_use_mega = 0;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
 }
@@ -261,6 +262,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.barriers_per_launch = 6 * d.layers + 1;
         p.stamps = s->stamps;
         p.depth = g_mega_depth;
+        p.debug = g_mega_debug;
         if (int rc = launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream))) return rc;
         if (launches) *launches = 1;
         return LEMOQ_OK;

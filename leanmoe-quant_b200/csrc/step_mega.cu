@@ -39,6 +39,7 @@ constexpr int kMegaStages = 3;
 constexpr int kMegaStageBytes = 4224;  // 2 rows x 2048 codes + 2 x 32 bytes of scales, padded to 128
 constexpr int kMegaScratchBytes = 28672;
 constexpr int NCH = 4;  // activations up to 2048 wide
+constexpr int kMegaMaxLayers = 33;  // layer descriptors kept in shared memory (layers + 1)
 constexpr int kMaxSplits = 9;   // attention splits per head the merge is unrolled for
 constexpr uint32_t kBarrierSpinLimit = 1u << 24;
 
@@ -97,6 +98,11 @@ __device__ __forceinline__ void substamp(const MegaParams& p, int l, int idx) {
 
 // SM cycle counter of block 0 / thread 0 into the extra stamp slots 32.. (profiling; last writer wins).
 __device__ __forceinline__ void dbg_clock(const MegaParams& p, int idx) {
+#ifndef LEMOQ_MEGA_PROFILE
+    (void)p;
+    (void)idx;
+    return;
+#endif
     if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.stamps[6 * p.layers + 2 + 32 + idx] = clock64();
 }
 
@@ -163,7 +169,7 @@ __device__ __forceinline__ void dp_rows(float (&acc)[R], const unsigned char* co
     const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int c = 0; c < NCH; ++c) {
         const int lc = c * 32 + lane;
         if (lc < nlc) {
@@ -252,11 +258,17 @@ __device__ __forceinline__ void build_stream_table(StreamTable& t, const MegaPar
     set(KIND_F, 1, LEMOQ_FIELD(dn_scale), gb, sps * F, gb, H * gb, 0);
     t.ncopies[KIND_F] = 2;  // per routed expert of the stage
     t.tx[KIND_F] = F + gb;  // per routed expert of the stage
+    if (p.debug & 1) {  // timing experiment (wrong results): no separate copies of the scales
+        t.ncopies[KIND_A] = 1; t.tx[KIND_A] = 2 * H;
+        t.ncopies[KIND_C] = 1; t.tx[KIND_C] = 2 * A;
+        t.ncopies[KIND_E] = 2; t.tx[KIND_E] = 2 * H;
+    }
 }
 
 struct WarpStream {
     const MegaParams* P;
     const StreamTable* T;
+    const MegaLayer* LS;      // layer descriptors in shared memory
     WarpRing<kMegaStages> ring;
     const unsigned char* my;  // generic pointer to this warp's stage 0
     int wg, G, lane;
@@ -272,7 +284,8 @@ struct WarpStream {
     // issue cursor: layer, kind, tasks left in the kind, task index, routed-expert slot, row inside the expert (E)
     int c_layer, c_kind, c_left, c_task, c_slot, c_n;
 
-    __device__ __forceinline__ int count(int n) const { return n > wg ? (n - wg + G - 1) / G : 0; }
+    __device__ __noinline__ static int count_of(int n, int wg, int G) { return n > wg ? (n - wg + G - 1) / G : 0; }
+    __device__ __forceinline__ int count(int n) const { return count_of(n, wg, G); }
     __device__ __forceinline__ int kind_cnt(int k) const {
         int v = cnt[0];
 #pragma unroll
@@ -345,7 +358,7 @@ struct WarpStream {
             __syncwarp();
             if (lane < static_cast<int>(T->ncopies[c_kind]) * nsl) {
                 const CopyDesc d = T->copy[c_kind][ci];
-                const char* base = *reinterpret_cast<const char* const*>(reinterpret_cast<const char*>(P->L + c_layer) + d.field);
+                const char* base = *reinterpret_cast<const char* const*>(reinterpret_cast<const char*>(LS + c_layer) + d.field);
                 const uint32_t t = c_kind == KIND_E ? c_n : c_task;
                 const uint64_t off = static_cast<uint64_t>(c_kind >= KIND_E ? expert : 0) * d.e_stride +
                                      static_cast<uint64_t>(t) * d.t_stride + d.cst;
@@ -437,73 +450,78 @@ __device__ __noinline__ TopK warp_topk(const __half* __restrict__ logits, int E,
 }
 
 // ---------------------------------------------------------------------------------------------
-// attention phase (one (head, split) unit per block): writes the (m, l, acc[D]) partial of its unit
+// attention phase (one (head, split) unit per block; head_dim 128, int8 KV with per-token scales)
 // ---------------------------------------------------------------------------------------------
+// Scores: one LANE per cached position.  The lane reads its position's 128 codes as eight 128-bit words
+// and multiplies them with the digit planes of the roped query through dp4a (the planes sit in shared
+// memory and are read as broadcasts), so a warp scores 32 positions with no shuffle at all.
+// Values: the 32 probabilities of the warp go through shared memory; each lane then owns four output
+// dimensions and walks the 32 positions, reading 4 codes (a coalesced 128-byte row per position).
+// The block's warps are merged in shared memory, the block writes the (m, l, acc[128]) partial of its
+// unit, and the block that arrives last at the head's counter merges the splits of the head.
+constexpr int kHeadDim = 128;
+
 struct AttnScratch {
-    float q[128];
-    float kx[128];
-    float red[40];
+    float q[kHeadDim];
+    float kx[kHeadDim];
+    float red[2 * kMegaWarps];
+    float amax[8];
     float wm[kMegaWarps];
     float wl[kMegaWarps];
-    float wacc[kMegaWarps][132];
+    float wacc[kMegaWarps][kHeadDim];
+    float pbuf[kMegaWarps][32];
+    __align__(16) uint32_t qplanes[3 * 8 * 4 + 8];
+    int last_flag;
 };
 
-template <int D>
-__device__ __forceinline__ __half rope_one(const float* __restrict__ xs, int d, const __half* __restrict__ cos,
-                                           const __half* __restrict__ sin) {
-    const float x = xs[d];
-    const float rot = d < D / 2 ? -xs[d + D / 2] : xs[d - D / 2];
-    return __float2half_rn(__fadd_rn(__fmul_rn(x, __half2float(cos[d])), __fmul_rn(rot, __half2float(sin[d]))));
+// What every layer's attention phase shares (computed once per step).
+struct AttnConst {
+    int pos;      // position of the new token (clamped into the cache)
+    int n_start;  // this block's slice of the cached positions
+    int n_end;
+    int owner;    // the slice contains the new token: this block writes its K/V row
+};
+
+__device__ __forceinline__ float rope_elem(const float* __restrict__ xs, int d, float c, float s) {
+    const float rot = d < kHeadDim / 2 ? -xs[d + kHeadDim / 2] : xs[d - kHeadDim / 2];
+    return __half2float(__float2half_rn(__fadd_rn(__fmul_rn(xs[d], c), __fmul_rn(rot, s))));
 }
 
-template <int D, bool INT8>
-__device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLayer& L, AttnScratch& sm) {
-    constexpr int LPP = D / 16;   // lanes per position
-    constexpr int GW = 32 / LPP;  // position groups per warp
+__device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLayer& L, AttnScratch& sm, const AttnConst ac,
+                                             const float* __restrict__ cs /* cos[128], sin[128] of the position */) {
+    constexpr int D = kHeadDim;
     const int unit = blockIdx.x;
     if (unit >= p.heads * p.splits) return;
     const int h = unit / p.splits, split = unit - h * p.splits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sub = lane % LPP, grp = lane / LPP;
     const int A = p.heads * D;
-
-    int n_filled = *p.filled;
-    if (n_filled < 0 || n_filled > p.S) {
-        if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_LENGTH);
-        n_filled = n_filled < 0 ? 0 : p.S;
-    }
-    const int chunk = (n_filled + p.splits - 1) / p.splits;
-    const int n_start = split * chunk;
-    const int n_end = min(n_start + chunk, n_filled);
-    int64_t pos = *p.cache_position;
-    const bool pos_ok = pos >= 0 && pos < p.S;
-    if (!pos_ok) {
-        if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_POSITION);
-        pos = pos < 0 ? 0 : p.S - 1;
-    }
-    const bool owner = pos_ok && pos >= n_start && pos < n_end;
-    const __half* cos = p.rope_cos + pos * D;
-    const __half* sin = p.rope_sin + pos * D;
     const int64_t hs = static_cast<int64_t>(p.S) * D;
     int8_t* kc = L.kc + h * hs;
     int8_t* vc = L.vc + h * hs;
     __half* ks = L.ks + static_cast<int64_t>(h) * p.S;
     __half* vs = L.vs + static_cast<int64_t>(h) * p.S;
-    __half* kh = L.keys + h * hs;
-    __half* vh = L.values + h * hs;
 
-    // sum of squares of the q row (and of the k row for the owner) in one block reduction
+    // ---- q (and, for the owner, the new K/V row): RMSNorm over all heads, RoPE, int8 row -------------
     float ssq = 0.f, ssk = 0.f;
-    for (int i = tid * 8; i < A; i += blockDim.x * 8) {
+#pragma unroll 1
+    for (int i = tid * 8; i < A; i += kMegaThreads * 8) {
+        const uint4 qv = ld_cg16(p.qkv + i);
+        const uint4 kv = ld_cg16(p.qkv + A + i);
         float f[8];
-        unpack8_h(ld_cg16(p.qkv + i), f);
+        unpack8_h(qv, f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) ssq = fmaf(f[j], f[j], ssq);
-        if (owner) {
-            unpack8_h(ld_cg16(p.qkv + A + i), f);
+        unpack8_h(kv, f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ssk = fmaf(f[j], f[j], ssk);
-        }
+        for (int j = 0; j < 8; ++j) ssk = fmaf(f[j], f[j], ssk);
+    }
+    __half qraw = __float2half_rn(0.f), kraw = qraw, vraw = qraw, qw = qraw, kw = qraw;
+    if (tid < D) {
+        qraw = __ldcg(p.qkv + h * D + tid);
+        kraw = __ldcg(p.qkv + A + h * D + tid);
+        vraw = __ldcg(p.qkv + 2 * A + h * D + tid);
+        qw = L.q_norm[h * D + tid];
+        kw = L.k_norm[h * D + tid];
     }
     ssq = warp_sum(ssq);
     ssk = warp_sum(ssk);
@@ -513,196 +531,157 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
     }
     __syncthreads();
     float tq = 0.f, tk = 0.f;
+#pragma unroll 1
     for (int w = 0; w < kMegaWarps; ++w) {
         tq += sm.red[w];
         tk += sm.red[kMegaWarps + w];
     }
-    const float rstd_q = 1.0f / sqrtf(tq / static_cast<float>(A) + p.eps);
-    const float rstd_k = 1.0f / sqrtf(tk / static_cast<float>(A) + p.eps);
     if (tid < D) {
-        sm.q[tid] = norm_elem(__ldcg(p.qkv + h * D + tid), rstd_q, L.q_norm[h * D + tid]);
-        if (owner) sm.kx[tid] = norm_elem(__ldcg(p.qkv + A + h * D + tid), rstd_k, L.k_norm[h * D + tid]);
+        sm.q[tid] = norm_elem(qraw, 1.0f / sqrtf(tq / static_cast<float>(A) + p.eps), qw);
+        sm.kx[tid] = norm_elem(kraw, 1.0f / sqrtf(tk / static_cast<float>(A) + p.eps), kw);
     }
     __syncthreads();
-    float qd = 0.f;
-    __half kn = __float2half_rn(0.f), vn = __float2half_rn(0.f);
+    float qd = 0.f, kn = 0.f;
     if (tid < D) {
-        qd = __half2float(rope_one<D>(sm.q, tid, cos, sin));
-        if (owner) {
-            kn = rope_one<D>(sm.kx, tid, cos, sin);
-            vn = __ldcg(p.qkv + 2 * A + h * D + tid);
-            kh[pos * D + tid] = kn;
-            vh[pos * D + tid] = vn;
+        qd = rope_elem(sm.q, tid, cs[tid], cs[D + tid]);
+        kn = rope_elem(sm.kx, tid, cs[tid], cs[D + tid]);
+        if (ac.owner) {
+            L.keys[h * hs + static_cast<int64_t>(ac.pos) * D + tid] = __float2half_rn(kn);
+            L.values[h * hs + static_cast<int64_t>(ac.pos) * D + tid] = vraw;
+            const float ak = warp_max(fabsf(kn)), av = warp_max(fabsf(__half2float(vraw)));
+            if (lane == 0) {
+                sm.amax[warp] = ak;
+                sm.amax[4 + warp] = av;
+            }
         }
     }
-    float amk = 0.f, amv = 0.f;
-    if (owner && INT8) {
-        amk = warp_max(tid < D ? fabsf(__half2float(kn)) : 0.f);
-        amv = warp_max(tid < D ? fabsf(__half2float(vn)) : 0.f);
-        if (lane == 0 && warp < (D + 31) / 32) {
-            sm.wm[warp] = amk;
-            sm.wl[warp] = amv;
-        }
-    }
-    __syncthreads();  // everyone has read sm.q (un-rotated) and the owner's partial maxima are in place
-    if (tid < D) sm.q[tid] = qd;
-    if (owner && INT8) {
-        amk = 0.f;
-        amv = 0.f;
-        for (int w = 0; w < (D + 31) / 32; ++w) {
-            amk = fmaxf(amk, sm.wm[w]);
-            amv = fmaxf(amv, sm.wl[w]);
-        }
-        const float sk = amk > 0.f ? __fdiv_rn(amk, 127.0f) : 1.0f;
-        const float sv = amv > 0.f ? __fdiv_rn(amv, 127.0f) : 1.0f;
-        if (tid < D) {
-            const float qk = fminf(fmaxf(rintf(__fdiv_rn(__half2float(kn), sk)), -127.0f), 127.0f);
-            const float qv = fminf(fmaxf(rintf(__fdiv_rn(__half2float(vn), sv)), -127.0f), 127.0f);
-            kc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qk));
-            vc[pos * D + tid] = static_cast<int8_t>(static_cast<int>(qv));
-        }
-        if (tid == 0) {
-            ks[pos] = __float2half_rn(sk);
-            vs[pos] = __float2half_rn(sv);
+    __syncthreads();  // the un-rotated q has been read by everyone; the owner's maxima are in place
+    if (tid < D) {
+        sm.q[tid] = qd * p.qk_scale_log2;
+        if (ac.owner) {
+            const float amk = fmaxf(fmaxf(sm.amax[0], sm.amax[1]), fmaxf(sm.amax[2], sm.amax[3]));
+            const float amv = fmaxf(fmaxf(sm.amax[4], sm.amax[5]), fmaxf(sm.amax[6], sm.amax[7]));
+            const float sk = amk > 0.f ? __fdiv_rn(amk, 127.0f) : 1.0f;
+            const float sv = amv > 0.f ? __fdiv_rn(amv, 127.0f) : 1.0f;
+            const float qk = fminf(fmaxf(rintf(__fdiv_rn(kn, sk)), -127.0f), 127.0f);
+            const float qv = fminf(fmaxf(rintf(__fdiv_rn(__half2float(vraw), sv)), -127.0f), 127.0f);
+            kc[static_cast<int64_t>(ac.pos) * D + tid] = static_cast<int8_t>(static_cast<int>(qk));
+            vc[static_cast<int64_t>(ac.pos) * D + tid] = static_cast<int8_t>(static_cast<int>(qv));
+            if (tid == 0) {
+                ks[ac.pos] = __float2half_rn(sk);
+                vs[ac.pos] = __float2half_rn(sv);
+            }
         }
     }
     __threadfence_block();
     __syncthreads();
+    if (warp == 0) {  // the scaled, roped q as digit planes: 8 lane chunks of 16 dims
+        const float f[4] = {sm.q[4 * lane], sm.q[4 * lane + 1], sm.q[4 * lane + 2], sm.q[4 * lane + 3]};
+        quantise_item(sm.qplanes, 8, lane, true, f);
+    }
+    __syncthreads();
 
-    float q[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) q[j] = sm.q[sub * 16 + j];
+    // ---- scores and values: each warp takes blocks of 32 positions --------------------------------------
     float m_i = -INFINITY, l_i = 0.f;
-    float acc[16];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* qsx = reinterpret_cast<const float*>(sm.qplanes + 3 * 8 * 4);
+#pragma unroll 1
+    for (int base = ac.n_start + warp * 32; base < ac.n_end; base += kMegaWarps * 32) {
+        const int n = min(base + lane, ac.n_end - 1);
+        const bool has = base + lane < ac.n_end;
+        uint4 kw8[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-
-    constexpr int GROUPS = kMegaWarps * GW;
-    const int group = warp * GW + grp;
-    for (int base = n_start; base < n_end; base += 2 * GROUPS) {
-        const int n0 = base + group, n1 = n0 + GROUPS;
-        const bool has0 = n0 < n_end, has1 = n1 < n_end;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        uint4 k0a = z, k0b = z, v0a = z, v0b = z, k1a = z, k1b = z, v1a = z, v1b = z;
-        float ks0 = 1.f, vs0 = 1.f, ks1 = 1.f, vs1 = 1.f;
-        if (INT8) {
-            if (has0) {
-                k0a = ld_cg16(kc + static_cast<int64_t>(n0) * D + sub * 16);
-                v0a = ld_cg16(vc + static_cast<int64_t>(n0) * D + sub * 16);
-                ks0 = __half2float(__ldcg(ks + n0));
-                vs0 = __half2float(__ldcg(vs + n0));
-            }
-            if (has1) {
-                k1a = ld_cg16(kc + static_cast<int64_t>(n1) * D + sub * 16);
-                v1a = ld_cg16(vc + static_cast<int64_t>(n1) * D + sub * 16);
-                ks1 = __half2float(__ldcg(ks + n1));
-                vs1 = __half2float(__ldcg(vs + n1));
-            }
-        } else {
-            if (has0) {
-                k0a = ld_cg16(kh + static_cast<int64_t>(n0) * D + sub * 16);
-                k0b = ld_cg16(kh + static_cast<int64_t>(n0) * D + sub * 16 + 8);
-                v0a = ld_cg16(vh + static_cast<int64_t>(n0) * D + sub * 16);
-                v0b = ld_cg16(vh + static_cast<int64_t>(n0) * D + sub * 16 + 8);
-            }
-            if (has1) {
-                k1a = ld_cg16(kh + static_cast<int64_t>(n1) * D + sub * 16);
-                k1b = ld_cg16(kh + static_cast<int64_t>(n1) * D + sub * 16 + 8);
-                v1a = ld_cg16(vh + static_cast<int64_t>(n1) * D + sub * 16);
-                v1b = ld_cg16(vh + static_cast<int64_t>(n1) * D + sub * 16 + 8);
+        for (int c = 0; c < 8; ++c) kw8[c] = ld_cg16(kc + static_cast<int64_t>(n) * D + c * 16);
+        const float kscale = __half2float(__ldcg(ks + n));
+        const float vscale = __half2float(__ldcg(vs + n));
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const uint4 x0 = *reinterpret_cast<const uint4*>(sm.qplanes + (0 * 8 + c) * 4);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(sm.qplanes + (1 * 8 + c) * 4);
+            const uint4 x2 = *reinterpret_cast<const uint4*>(sm.qplanes + (2 * 8 + c) * 4);
+            const uint4 w = kw8[c];
+            int s0 = __dp4a(static_cast<int>(w.x), static_cast<int>(x0.x), 0);
+            int s1 = __dp4a(static_cast<int>(w.x), static_cast<int>(x1.x), 0);
+            int s2 = __dp4a(static_cast<int>(w.x), static_cast<int>(x2.x), 0);
+            s0 = __dp4a(static_cast<int>(w.y), static_cast<int>(x0.y), s0);
+            s1 = __dp4a(static_cast<int>(w.y), static_cast<int>(x1.y), s1);
+            s2 = __dp4a(static_cast<int>(w.y), static_cast<int>(x2.y), s2);
+            s0 = __dp4a(static_cast<int>(w.z), static_cast<int>(x0.z), s0);
+            s1 = __dp4a(static_cast<int>(w.z), static_cast<int>(x1.z), s1);
+            s2 = __dp4a(static_cast<int>(w.z), static_cast<int>(x2.z), s2);
+            s0 = __dp4a(static_cast<int>(w.w), static_cast<int>(x0.w), s0);
+            s1 = __dp4a(static_cast<int>(w.w), static_cast<int>(x1.w), s1);
+            s2 = __dp4a(static_cast<int>(w.w), static_cast<int>(x2.w), s2);
+            const float t = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
+            s = fmaf(t, qsx[c], s);
+        }
+        s = has ? s * kscale : -INFINITY;
+        const float m_new = fmaxf(m_i, warp_max(s));  // finite: lane 0 always has a position
+        const float alpha = exp2f(m_i - m_new);
+        const float pw = has ? exp2f(s - m_new) : 0.f;
+        l_i = fmaf(l_i, alpha, warp_sum(pw));
+        m_i = m_new;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] *= alpha;
+        __syncwarp();
+        sm.pbuf[warp][lane] = pw * vscale;
+        __syncwarp();
+        const int cnt = min(32, ac.n_end - base);
+        const int8_t* vrow = vc + static_cast<int64_t>(base) * D + lane * 4;
+#pragma unroll 1
+        for (int j0 = 0; j0 < cnt; j0 += 16) {
+            uint32_t vw[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) vw[j] = __ldcg(reinterpret_cast<const uint32_t*>(vrow + static_cast<int64_t>(min(j0 + j, cnt - 1)) * D));
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float pj = j0 + j < cnt ? sm.pbuf[warp][j0 + j] : 0.f;
+                acc[0] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] & 0xffu)), acc[0]);
+                acc[1] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 8) & 0xffu)), acc[1]);
+                acc[2] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 16) & 0xffu)), acc[2]);
+                acc[3] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] >> 24)), acc[3]);
             }
         }
-        float d0, d1;
-        if (INT8) {
-            d0 = dot16_s8(k0a, q);
-            d1 = dot16_s8(k1a, q);
-        } else {
-            d0 = dot8_h(k0a, &q[0]) + dot8_h(k0b, &q[8]);
-            d1 = dot8_h(k1a, &q[0]) + dot8_h(k1b, &q[8]);
-        }
-#pragma unroll
-        for (int o = LPP / 2; o > 0; o >>= 1) {
-            d0 += __shfl_xor_sync(0xffffffffu, d0, o);
-            d1 += __shfl_xor_sync(0xffffffffu, d1, o);
-        }
-        auto step = [&](float s, float v_scale, const uint4& va, const uint4& vb) {
-            const float m_new = fmaxf(m_i, s);
-            const float alpha = exp2f(m_i - m_new);
-            const float pw = exp2f(s - m_new);
-            l_i = fmaf(l_i, alpha, pw);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] *= alpha;
-            if (INT8) {
-                axpy16_s8(va, pw * v_scale, acc);
-            } else {
-                float f[16];
-                unpack8_h(va, &f[0]);
-                unpack8_h(vb, &f[8]);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = fmaf(pw, f[j], acc[j]);
-            }
-            m_i = m_new;
-        };
-        if (has0) step(INT8 ? d0 * p.qk_scale_log2 * ks0 : d0 * p.qk_scale_log2, vs0, v0a, v0b);
-        if (has1) step(INT8 ? d1 * p.qk_scale_log2 * ks1 : d1 * p.qk_scale_log2, vs1, v1a, v1b);
     }
-
-    // merge the position groups of the warp (fixed xor order), then the warps of the block
-#pragma unroll
-    for (int o = LPP; o < 32; o <<= 1) {
-        const float mo = __shfl_xor_sync(0xffffffffu, m_i, o);
-        const float lo = __shfl_xor_sync(0xffffffffu, l_i, o);
-        const float mn = fmaxf(m_i, mo);
-        const float base = mn > -INFINITY ? mn : 0.f;
-        const float wa = exp2f(m_i - base), wb = exp2f(mo - base);
-        l_i = l_i * wa + lo * wb;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float ao = __shfl_xor_sync(0xffffffffu, acc[j], o);
-            acc[j] = acc[j] * wa + ao * wb;
-        }
-        m_i = mn;
-    }
-    if (lane < LPP) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) sm.wacc[warp][lane * 16 + j] = acc[j];
-        if (lane == 0) {
-            sm.wm[warp] = m_i;
-            sm.wl[warp] = l_i;
-        }
+    // ---- merge the warps of the block ----------------------------------------------------------------------
+    *reinterpret_cast<float4*>(&sm.wacc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (lane == 0) {
+        sm.wm[warp] = m_i;
+        sm.wl[warp] = l_i;
     }
     __syncthreads();
     // partial layout: acc[(h*S + split)*D + d], then the (m, l) pairs
-    float* part = p.attn_part + (static_cast<int64_t>(h) * p.splits + split) * D;
-    float* part_ml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + (static_cast<int64_t>(h) * p.splits + split) * 2;
     if (tid < D) {
         float big = -INFINITY;
+#pragma unroll 1
         for (int w = 0; w < kMegaWarps; ++w) big = fmaxf(big, sm.wm[w]);
-        const float base = big > -INFINITY ? big : 0.f;
+        const float bs = big > -INFINITY ? big : 0.f;
         float a = 0.f, l = 0.f;
+#pragma unroll 1
         for (int w = 0; w < kMegaWarps; ++w) {
-            const float wt = exp2f(sm.wm[w] - base);
+            const float wt = exp2f(sm.wm[w] - bs);
             a = fmaf(sm.wacc[w][tid], wt, a);
             l = fmaf(sm.wl[w], wt, l);
         }
-        part[tid] = a;
+        p.attn_part[(static_cast<int64_t>(h) * p.splits + split) * D + tid] = a;
         if (tid == 0) {
-            part_ml[0] = big;
-            part_ml[1] = l;
+            float* ml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + (static_cast<int64_t>(h) * p.splits + split) * 2;
+            ml[0] = big;
+            ml[1] = l;
         }
     }
-    // The block that arrives last at its head's counter merges the splits of the head: every block then
-    // reads the finished 2*D bytes per head instead of all partials.
+    // ---- the block that arrives last at its head's counter merges the splits of the head -------------------
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned int prev = atomicAdd(p.attn_counters + h, 1u);
         const bool is_last = prev + 1u == static_cast<unsigned int>(p.splits);
         if (is_last) p.attn_counters[h] = 0u;  // everyone of this layer has arrived: ready for the next one
-        sm.red[0] = is_last ? 1.f : 0.f;
+        sm.last_flag = is_last ? 1 : 0;
     }
     __syncthreads();
-    if (sm.red[0] != 0.f && tid < D) {
+    if (sm.last_flag != 0 && tid < D) {
         __threadfence();
         const float* hacc = p.attn_part + static_cast<int64_t>(h) * p.splits * D + tid;
         const float* hml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + static_cast<int64_t>(h) * p.splits * 2;
@@ -830,7 +809,7 @@ __device__ __noinline__ void prepare_act(uint32_t* dst, const MegaParams& p, int
 }
 
 // L2 prefetch of a byte range by the whole block (128-byte lines).
-__device__ __forceinline__ void prefetch_l2(const void* ptr, int64_t bytes) {
+__device__ __noinline__ void prefetch_l2(const void* ptr, int64_t bytes) {
     const char* c = reinterpret_cast<const char*>(ptr);
     for (int64_t off = static_cast<int64_t>(threadIdx.x) * 128; off < bytes; off += static_cast<int64_t>(kMegaThreads) * 128)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
@@ -851,10 +830,20 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
     float* red = reinterpret_cast<float*>(scratch + 7168);   // reduction scratch
     float* h2f = reinterpret_cast<float*>(scratch + 7680);   // fp32 h2, lane-major, for the fp16 router rows (8 KB)
     StreamTable& table = *reinterpret_cast<StreamTable*>(scratch + kMegaScratchBytes);
+    float* cs_s = reinterpret_cast<float*>(scratch + kMegaScratchBytes + ((sizeof(StreamTable) + 127) & ~size_t(127)));  // cos, sin
+    int* route_s = reinterpret_cast<int*>(cs_s + 2 * kHeadDim);  // routed expert ids and weights of the layer
+    MegaLayer* layers_s = reinterpret_cast<MegaLayer*>(route_s + 64);  // the layer descriptors (layers + 1 of them)
+    {
+        const uint64_t* src = reinterpret_cast<const uint64_t*>(p.L);
+        uint64_t* dst = reinterpret_cast<uint64_t*>(layers_s);
+        const int words = (p.layers + 1) * static_cast<int>(sizeof(MegaLayer) / 8);
+        for (int i = threadIdx.x; i < words; i += kMegaThreads) dst[i] = src[i];
+    }
 
     WarpStream ws;
     ws.P = &p;
     ws.T = &table;
+    ws.LS = layers_s;
     ws.G = gridDim.x * kMegaWarps;
     ws.wg = warp * gridDim.x + blockIdx.x;
     ws.lane = lane;
@@ -875,7 +864,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
     ws.ids_reg = 0;
     __syncthreads();
     ws.start();
-    ws.pump();
 
     GridBarrier bar;
     bar.counter = p.bar_counter;
@@ -888,16 +876,36 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
     const int sbase = lane16 / p.group, sstride = 512 / p.group;
     const int vec_words = 3 * (p.F / 16) * 4 + p.F / 16;  // one quantised expert activation vector
 
-    // This block's slice of the KV cache is the same in every layer: prefetch it into L2 one phase ahead.
+    // Position, cache slice and RoPE row are the same in every layer of the step.
+    AttnConst ac;
     int kv_first = 0, kv_count = 0;
-    if (static_cast<int>(blockIdx.x) < p.heads * p.splits) {
+    {
         int nf = *p.filled;
-        nf = nf < 0 ? 0 : (nf > p.S ? p.S : nf);
-        const int h = blockIdx.x / p.splits, split = blockIdx.x - h * p.splits;
+        int64_t pos = *p.cache_position;
+        if (nf < 0 || nf > p.S) {
+            if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_LENGTH);
+            nf = nf < 0 ? 0 : p.S;
+        }
+        const bool pos_ok = pos >= 0 && pos < p.S;
+        if (!pos_ok) {
+            if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_POSITION);
+            pos = pos < 0 ? 0 : p.S - 1;
+        }
+        const int unit = blockIdx.x < static_cast<unsigned int>(p.heads * p.splits) ? blockIdx.x : 0;
+        const int h = unit / p.splits, split = unit - h * p.splits;
         const int chunk = (nf + p.splits - 1) / p.splits;
-        const int n0 = split * chunk, n1 = min(n0 + chunk, nf);
-        kv_first = h * p.S + n0;
-        kv_count = n1 > n0 ? n1 - n0 : 0;
+        ac.pos = static_cast<int>(pos);
+        ac.n_start = split * chunk;
+        ac.n_end = min(ac.n_start + chunk, nf);
+        ac.owner = pos_ok && pos >= ac.n_start && pos < ac.n_end;
+        if (static_cast<int>(blockIdx.x) < p.heads * p.splits) {
+            kv_first = h * p.S + ac.n_start;
+            kv_count = ac.n_end > ac.n_start ? ac.n_end - ac.n_start : 0;
+        }
+        if (threadIdx.x < kHeadDim) {
+            cs_s[threadIdx.x] = __half2float(p.rope_cos[pos * kHeadDim + threadIdx.x]);
+            cs_s[kHeadDim + threadIdx.x] = __half2float(p.rope_sin[pos * kHeadDim + threadIdx.x]);
+        }
     }
 
     const __half* x_prev = p.embed + (*p.token) * static_cast<int64_t>(p.H);
@@ -907,7 +915,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 
 #pragma unroll 1
     for (int step = 0; step < nphases; ++step) {
-        const MegaLayer& L = p.L[l];
+        const MegaLayer& L = layers_s[l];
         const bool last = l == p.layers;
         int ntasks = 0, K = p.H, nst = 1;
         if (ph == 0) dbg_clock(p, 24);
@@ -915,33 +923,30 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
         // ---- block-wide preparation of the phase -----------------------------------------------------
         if (ph == 0 || ph == 2 || ph == 3) {
             if (ph == 0 && !last && kv_count > 0) {
-                const int64_t eb = p.kv_int8 ? 1 : 2;
-                const void* kp = p.kv_int8 ? static_cast<const void*>(L.kc + static_cast<int64_t>(kv_first) * p.D)
-                                           : static_cast<const void*>(L.keys + static_cast<int64_t>(kv_first) * p.D);
-                const void* vp = p.kv_int8 ? static_cast<const void*>(L.vc + static_cast<int64_t>(kv_first) * p.D)
-                                           : static_cast<const void*>(L.values + static_cast<int64_t>(kv_first) * p.D);
-                prefetch_l2(kp, static_cast<int64_t>(kv_count) * p.D * eb);
-                prefetch_l2(vp, static_cast<int64_t>(kv_count) * p.D * eb);
-                if (p.kv_int8) {
-                    prefetch_l2(L.ks + kv_first, static_cast<int64_t>(kv_count) * 2);
-                    prefetch_l2(L.vs + kv_first, static_cast<int64_t>(kv_count) * 2);
-                }
+                prefetch_l2(L.kc + static_cast<int64_t>(kv_first) * p.D, static_cast<int64_t>(kv_count) * p.D);
+                prefetch_l2(L.vc + static_cast<int64_t>(kv_first) * p.D, static_cast<int64_t>(kv_count) * p.D);
+                prefetch_l2(L.ks + kv_first, static_cast<int64_t>(kv_count) * 2);
+                prefetch_l2(L.vs + kv_first, static_cast<int64_t>(kv_count) * 2);
             }
-            if (ph == 0) dbg_clock(p, 26);
             if (ph == 2) K = A;
             prepare_norm(p, ph == 0 ? 0 : 8, xq_s, red, ph == 0 ? x_prev : (ph == 2 ? p.attn : p.xa),
                          ph == 0 ? L.ln1 : (ph == 2 ? nullptr : L.ln2), K, p.eps, ph == 3 ? h2f : nullptr);
             ntasks = ph == 0 ? (last ? ws.cnt_lm : ws.cnt[KIND_A]) : (ph == 2 ? ws.cnt[KIND_C] : ws.cnt[KIND_D]);
         } else if (ph == 1) {
             AttnScratch& sm = *reinterpret_cast<AttnScratch*>(scratch);
-            if (p.kv_int8) attention_phase<128, true>(p, L, sm);
-            else attention_phase<128, false>(p, L, sm);
+            attention_phase(p, L, sm, ac, cs_s);
         } else if (ph == 4) {
-            const TopK tk = warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane);
-            ws.ids_reg = tk.id;
-            tw_reg = tk.w;
+            dbg_clock(p, 30);
+            // one warp routes, the others pick the result up from shared memory
+            if (warp == 0) {
+                const TopK tk = warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane);
+                route_s[lane] = tk.id;
+                route_s[32 + lane] = __float_as_int(tk.w);
+            }
+            __syncthreads();
+            ws.ids_reg = route_s[lane];
+            tw_reg = __int_as_float(route_s[32 + lane]);
             ws.ids_ready_layer = l;
-            ws.pump();
             if (blockIdx.x == 0 && warp == 0 && lane < p.K) {
                 p.top_i[static_cast<int64_t>(l) * p.K + lane] = ws.ids_reg;
                 p.top_w[lane] = __float2half_rn(tw_reg);
@@ -953,6 +958,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
             ntasks = ws.cnt[KIND_F];
             nst = (p.K + ws.sps - 1) / ws.sps;
         }
+        ws.pump();  // the one place besides release(): start of the step, and the expert rows once the routing is known
         substamp(p, l, 2 * ph);
         const int gK = K / p.group;
 
@@ -970,7 +976,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                     break;
                 }
                 if (ph == 3) {  // one fp16 router row against the fp32 h2
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < NCH; ++c) {
                         const int k0 = c * 512 + lane16;
                         if (k0 < p.H) {
@@ -1045,7 +1051,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 // ---------------------------------------------------------------------------------------------
 size_t mega_smem_bytes() {
     return static_cast<size_t>(kMegaWarps) * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 512 +
-           kMegaScratchBytes + sizeof(StreamTable);
+           kMegaScratchBytes + sizeof(StreamTable) + 128 + 2 * kHeadDim * sizeof(float) + 64 * sizeof(int) + kMegaMaxLayers * sizeof(MegaLayer);
 }
 
 bool mega_eligible(const lemoq_step_desc& d) {
@@ -1057,9 +1063,9 @@ bool mega_eligible(const lemoq_step_desc& d) {
     // one expert row of scales (gate/up rows and down rows are copied singly) must be a 16-byte multiple
     if (((d.hidden / g) * 2) % 16 != 0 || ((d.ffn / g) * 2) % 16 != 0) return false;
     if (d.ffn + 2 * (d.ffn / g) > kMegaStageBytes) return false;
-    if (d.head_dim != 128) return false;
+    if (d.head_dim != kHeadDim || !d.kv_int8) return false;  // the fp16-KV arm runs as chained kernels
     if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
-    if (d.vocab % 2 != 0) return false;
+    if (d.vocab % 2 != 0 || d.layers + 1 > kMegaMaxLayers) return false;
     const size_t vec_words = 3 * (d.ffn / 16) * 4 + d.ffn / 16;
     if (static_cast<size_t>(d.top_k) * vec_words * 4 > kMegaScratchBytes) return false;
     if (sizeof(AttnScratch) > kMegaScratchBytes) return false;

@@ -38,6 +38,7 @@ struct MegaParams {
     int64_t* top_i;
     float* attn_part;
     int barriers_per_launch;
+    int debug;                   // timing experiments (wrong results)
     int depth;                   // stages a warp keeps in flight (clamped to the ring size)
     unsigned long long* stamps;  // optional: 6*layers + 2 phase time stamps of the last step
 };

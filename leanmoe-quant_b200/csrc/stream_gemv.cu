@@ -23,6 +23,7 @@ int g_dot_mode = DOT_F16_FOLD;
 extern int g_step_skip_mask;
 extern int g_step_use_mega;
 extern int g_mega_depth;
+extern int g_mega_debug;
 int g_debug_skip_scale_copy = 0;  // timing experiments only: results are wrong when set
 
 // ---------------------------------------------------------------------------
@@ -372,6 +373,10 @@ int set_stream_tuning(int key, int value) {
     }
     if (key == 4) {
         g_step_use_mega = value;
+        return LEMOQ_OK;
+    }
+    if (key == 6) {
+        g_mega_debug = value;
         return LEMOQ_OK;
     }
     if (key == 5 && value >= 1 && value <= 8) {
