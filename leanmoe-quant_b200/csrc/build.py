@@ -22,7 +22,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
-]
+] + os.environ.get("LEMOQ_NVCC_EXTRA", "").split()  # e.g. -DLEMOQ_MEGA_PROFILE for the cycle stamps of the whole-step kernel
 
 
 def _newer(src: str, dst: str) -> bool:

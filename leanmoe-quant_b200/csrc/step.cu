@@ -127,7 +127,7 @@ namespace lemoq {
 int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
 int g_mega_debug = 0;      // lemoq_set_tuning key 6: timing experiments of the whole-step kernel (wrong results)
 int g_mega_depth = 8;      // lemoq_set_tuning key 5: stages a warp of the whole-step kernel keeps in flight (capped by its ring)
-int g_step_use_mega = 0;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
+int g_step_use_mega = 1;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
 }
 
 using namespace lemoq;

@@ -35,9 +35,9 @@ namespace lemoq {
 
 constexpr int kMegaWarps = 14;
 constexpr int kMegaThreads = kMegaWarps * 32;
-constexpr int kMegaStages = 3;
+constexpr int kMegaStages = 2;
 constexpr int kMegaStageBytes = 4224;  // 2 rows x 2048 codes + 2 x 32 bytes of scales, padded to 128
-constexpr int kMegaScratchBytes = 28672;
+constexpr int kMegaScratchBytes = 28672 + 16384 + 4096 + 128;  // planes, raw staging, norm weights, reductions
 constexpr int NCH = 4;  // activations up to 2048 wide
 constexpr int kMegaMaxLayers = 33;  // layer descriptors kept in shared memory (layers + 1)
 constexpr int kMaxSplits = 9;   // attention splits per head the merge is unrolled for
@@ -283,6 +283,10 @@ struct WarpStream {
     int ids_reg;              // lane k holds the k-th expert id of ids_ready_layer
     // issue cursor: layer, kind, tasks left in the kind, task index, routed-expert slot, row inside the expert (E)
     int c_layer, c_kind, c_left, c_task, c_slot, c_n;
+    // this lane's bulk copy of the current kind (lane c issues copy c; in kind F lane 2j + c copies for routed expert j)
+    const char* lc_base;
+    uint32_t lc_ts, lc_es, lc_bytes, lc_dst;
+    uint32_t k_tx, k_ncop;    // bytes and copies per task (per routed expert in kind F) of the current kind
 
     __device__ __noinline__ static int count_of(int n, int wg, int G) { return n > wg ? (n - wg + G - 1) / G : 0; }
     __device__ __forceinline__ int count(int n) const { return count_of(n, wg, G); }
@@ -301,6 +305,21 @@ struct WarpStream {
                 c_n -= P->F;
                 ++c_slot;
             }
+        }
+        const bool isF = c_kind == KIND_F;
+        const int ci = isF ? lane & 1 : lane;
+        k_tx = T->tx[c_kind];
+        k_ncop = T->ncopies[c_kind];
+        lc_bytes = 0;
+        lc_base = nullptr;
+        lc_ts = lc_es = lc_dst = 0;
+        if (ci < static_cast<int>(k_ncop)) {  // the table only describes the copies the kind has
+            const CopyDesc d = T->copy[c_kind][ci];
+            lc_base = *reinterpret_cast<const char* const*>(reinterpret_cast<const char*>(LS + c_layer) + d.field) + d.cst;
+            lc_ts = d.t_stride;
+            lc_es = d.e_stride;
+            lc_bytes = d.bytes;
+            lc_dst = d.dst + (isF ? (lane >> 1) * d.bytes : 0u);
         }
     }
     __device__ __forceinline__ void next_kind() {
@@ -351,18 +370,14 @@ struct WarpStream {
             const uint32_t dst = ring.stage(i_stage), bar = ring.bar(i_stage);
             const bool isF = c_kind == KIND_F;
             const int nsl = isF ? min(sps, P->K - c_slot) : 1;
-            const int j = isF ? lane >> 1 : 0;       // routed expert of the stage this lane copies for
-            const int ci = isF ? lane & 1 : lane;    // which copy of the kind
-            const int expert = __shfl_sync(0xffffffffu, ids_reg, (c_slot + j) & 31);
-            if (lane == 0) mbar_expect_tx(bar, T->tx[c_kind] * nsl);
+            // expert of this lane's copy (ignored by the kinds whose expert stride is zero)
+            const int expert = __shfl_sync(0xffffffffu, ids_reg, (c_slot + (isF ? lane >> 1 : 0)) & 31);
+            if (lane == 0) mbar_expect_tx(bar, k_tx * nsl);
             __syncwarp();
-            if (lane < static_cast<int>(T->ncopies[c_kind]) * nsl) {
-                const CopyDesc d = T->copy[c_kind][ci];
-                const char* base = *reinterpret_cast<const char* const*>(reinterpret_cast<const char*>(LS + c_layer) + d.field);
+            if (lane < static_cast<int>(k_ncop) * nsl) {
                 const uint32_t t = c_kind == KIND_E ? c_n : c_task;
-                const uint64_t off = static_cast<uint64_t>(c_kind >= KIND_E ? expert : 0) * d.e_stride +
-                                     static_cast<uint64_t>(t) * d.t_stride + d.cst;
-                bulk_g2s(dst + d.dst + j * d.bytes, base + off, d.bytes, bar);
+                const uint64_t off = static_cast<uint64_t>(expert) * lc_es + static_cast<uint64_t>(t) * lc_ts;
+                bulk_g2s(dst + lc_dst, lc_base + off, lc_bytes, bar);
             }
             i_stage = i_stage + 1 == kMegaStages ? 0 : i_stage + 1;
             ++inflight;
@@ -377,13 +392,24 @@ struct WarpStream {
         }
         return my + static_cast<size_t>(c_stage) * kMegaStageBytes;
     }
-    __device__ __forceinline__ void release() {
+    // the stage after the oldest one (both are then released in order)
+    __device__ __forceinline__ const unsigned char* acquire_next() {
+        const int s = c_stage + 1 == kMegaStages ? 0 : c_stage + 1;
+        const int par = c_stage + 1 == kMegaStages ? c_par ^ 1 : c_par;
+        if (!mbar_wait(ring.bar(s), par)) {
+            if (P->err_flag && lane == 0) atomicOr(P->err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+            return nullptr;
+        }
+        return my + static_cast<size_t>(s) * kMegaStageBytes;
+    }
+    __device__ __forceinline__ void release(int n) {  // the n oldest stages
         __syncwarp();
-        if (++c_stage == kMegaStages) {
-            c_stage = 0;
+        c_stage += n;
+        if (c_stage >= kMegaStages) {
+            c_stage -= kMegaStages;
             c_par ^= 1;
         }
-        --inflight;
+        inflight -= n;
         pump();
     }
 };
@@ -727,82 +753,69 @@ __device__ __forceinline__ float block_sum_once(float v, float* red) {
     return t;
 }
 
-constexpr int kPrepItems = 2;  // 4-element items per thread: covers vectors up to 8 * kMegaThreads wide
+// Scratch layout (bytes): [0, kRawOff) digit planes / attention scratch / reductions, then the raw fp16
+// staging of the phase's activation vectors (16 KB) and of the norm weights (4 KB).
+constexpr int kRawOff = 28672;
+constexpr int kRawBytes = 16384;
+constexpr int kNormWOff = kRawOff + kRawBytes;
+constexpr int kNormWBytes = 4096;
 
-// RMSNorm(row) * nw (just row when nw is null) -> digit planes at dst (and, when f32out is given, the fp32 values in the lane-major
-// layout ((c*4 + q)*32 + ln)*4 + r for k = c*512 + ln*16 + q*4 + r).  One global round trip: the raw
-// values stay in registers between the statistic and the normalisation.
-__device__ __noinline__ void prepare_norm(const MegaParams& p, int dbg, uint32_t* dst, float* red, const __half* __restrict__ row,
-                                             const __half* __restrict__ nw, int n, float eps, float* f32out) {
-    dbg_clock(p, dbg + 0);
-    uint2 xv[kPrepItems], wv[kPrepItems];
-    float ss = 0.f;
-#pragma unroll
-    for (int it = 0; it < kPrepItems; ++it) {
-        const int item = threadIdx.x + it * kMegaThreads;
-        xv[it] = make_uint2(0u, 0u);
-        wv[it] = make_uint2(0u, 0u);
-        if (item < n / 4) {
-            xv[it] = __ldcg(reinterpret_cast<const uint2*>(row + 4 * item));
-            if (nw != nullptr) wv[it] = *reinterpret_cast<const uint2*>(nw + 4 * item);
-        }
-        const __half* xh = reinterpret_cast<const __half*>(&xv[it]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float f = __half2float(xh[j]);
-            ss = fmaf(f, f, ss);
-        }
+// One routine prepares the activations of every weight phase.  Thread 0 brings `total` fp16 values
+// (and the RMSNorm weights, when given) into shared memory with bulk copies; everyone waits on the
+// copy's mbarrier; then the values are normalised (nw != null), quantised into digit planes
+// (vectors of 2^vshift values each, vector v at dst + v * vec_words) and, when f32out is given,
+// also stored as fp32 in the lane-major layout ((c*4 + q)*32 + ln)*4 + r for k = c*512 + ln*16 + q*4 + r.
+__device__ __noinline__ void prepare_vectors(unsigned char* scratch, uint32_t bar, int parity, const MegaParams& p,
+                                             const __half* __restrict__ src, const __half* __restrict__ nw, int total, int vshift,
+                                             uint32_t* dst, int vec_words, float* f32out) {
+    const __half* raw = reinterpret_cast<const __half*>(scratch + kRawOff);
+    const __half* nws = reinterpret_cast<const __half*>(scratch + kNormWOff);
+    float* red = reinterpret_cast<float*>(scratch + kNormWOff + kNormWBytes);
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(bar, static_cast<uint32_t>(2 * total * (nw != nullptr ? 2 : 1)));
+        bulk_g2s(smem_u32(raw), src, static_cast<uint32_t>(2 * total), bar);
+        if (nw != nullptr) bulk_g2s(smem_u32(nws), nw, static_cast<uint32_t>(2 * total), bar);
     }
-    dbg_clock(p, dbg + 1);
-    const float rstd = nw != nullptr ? 1.0f / sqrtf(block_sum_once(ss, red) / static_cast<float>(n) + eps) : 0.f;
-    dbg_clock(p, dbg + 2);
-#pragma unroll
-    for (int it = 0; it < kPrepItems; ++it) {
-        const int item = threadIdx.x + it * kMegaThreads;
-        if (item - (threadIdx.x & 31) < n / 4) {  // whole warps take part in the shuffles
-            const __half* xh = reinterpret_cast<const __half*>(&xv[it]);
-            const __half* wh = reinterpret_cast<const __half*>(&wv[it]);
-            float f[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) f[j] = nw != nullptr ? norm_elem(xh[j], rstd, wh[j]) : __half2float(xh[j]);
-            const bool on = item < n / 4;
-            quantise_item(dst, n / 16, item, on, f);
-            if (f32out != nullptr && on) {
-                const int k = 4 * item;
-                const int c = k >> 9, ln = (k & 511) >> 4, q = (k & 15) >> 2;
-                *reinterpret_cast<float4*>(f32out + (((c * 4 + q) * 32 + ln) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
-            }
-        }
+    if (!mbar_wait(bar, parity)) {
+        if (p.err_flag && threadIdx.x == 0) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
     }
-    dbg_clock(p, dbg + 3);
-    __syncthreads();
-    dbg_clock(p, dbg + 4);
-}
-
-// The K expert activation vectors (fp16, K x F) -> digit planes, vector `slot` at dst + slot * vec_words.
-__device__ __noinline__ void prepare_act(uint32_t* dst, const MegaParams& p, int vec_words) {
-    const int per = p.F / 4, total = p.K * per;  // items per vector / in all
-    for (int base = 0; base < total; base += 4 * kMegaThreads) {
-        uint2 xv[4];
+    const int items = total >> 2;
+    float rstd = 0.f;
+    if (nw != nullptr) {
+        float ss = 0.f;
+#pragma unroll 1
+        for (int item = threadIdx.x; item < items; item += kMegaThreads) {
+            const uint2 xv = *reinterpret_cast<const uint2*>(raw + 4 * item);
+            const __half* xh = reinterpret_cast<const __half*>(&xv);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int item = base + u * kMegaThreads + threadIdx.x;
-            xv[u] = make_uint2(0u, 0u);
-            if (item < total) xv[u] = __ldcg(reinterpret_cast<const uint2*>(p.act + 4 * static_cast<int64_t>(item)));
+            for (int j = 0; j < 4; ++j) ss = fmaf(__half2float(xh[j]), __half2float(xh[j]), ss);
         }
+        rstd = 1.0f / sqrtf(block_sum_once(ss, red) / static_cast<float>(total) + p.eps);
+    }
+    const int vmask = (1 << (vshift - 2)) - 1;  // items per vector - 1
+#pragma unroll 1
+    for (int item = threadIdx.x; item - static_cast<int>(threadIdx.x & 31) < items; item += kMegaThreads) {
+        const bool on = item < items;
+        float f[4] = {0.f, 0.f, 0.f, 0.f};
+        if (on) {
+            const uint2 xv = *reinterpret_cast<const uint2*>(raw + 4 * item);
+            const __half* xh = reinterpret_cast<const __half*>(&xv);
+            if (nw != nullptr) {
+                const uint2 wv = *reinterpret_cast<const uint2*>(nws + 4 * item);
+                const __half* wh = reinterpret_cast<const __half*>(&wv);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int item = base + u * kMegaThreads + threadIdx.x;
-            if (item - (threadIdx.x & 31) < total) {
-                const bool on = item < total;
-                const int slot = on ? item / per : 0;
-                const int within = item - slot * per;
-                const __half* xh = reinterpret_cast<const __half*>(&xv[u]);
-                float f[4];
+                for (int j = 0; j < 4; ++j) f[j] = norm_elem(xh[j], rstd, wh[j]);
+            } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) f[j] = __half2float(xh[j]);
-                quantise_item(dst + slot * vec_words, p.F / 16, within, on, f);
             }
+        }
+        const int vec = item >> (vshift - 2), within = item & vmask;
+        quantise_item(dst + vec * vec_words, 1 << (vshift - 4), within, on, f);
+        if (f32out != nullptr && on) {
+            const int k = 4 * item;
+            const int c = k >> 9, ln = (k & 511) >> 4, q = (k & 15) >> 2;
+            *reinterpret_cast<float4*>(f32out + (((c * 4 + q) * 32 + ln) << 2)) = make_float4(f[0], f[1], f[2], f[3]);
         }
     }
     __syncthreads();
@@ -827,7 +840,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
     unsigned char* scratch = smem + kMegaWarps * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 128;
     scratch = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(scratch) + 127) & ~uintptr_t(127));
     uint32_t* xq_s = reinterpret_cast<uint32_t*>(scratch);  // quantised activation vector (<= 6.7 KB)
-    float* red = reinterpret_cast<float*>(scratch + 7168);   // reduction scratch
     float* h2f = reinterpret_cast<float*>(scratch + 7680);   // fp32 h2, lane-major, for the fp16 router rows (8 KB)
     StreamTable& table = *reinterpret_cast<StreamTable*>(scratch + kMegaScratchBytes);
     float* cs_s = reinterpret_cast<float*>(scratch + kMegaScratchBytes + ((sizeof(StreamTable) + 127) & ~size_t(127)));  // cos, sin
@@ -856,6 +868,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
     ws.sps = min(min(4, p.K), kMegaStageBytes / (p.F + 2 * (p.F / p.group)));
     if (threadIdx.x == 0) build_stream_table(table, p, ws.sps);
     ws.ring.init(smem, warp, kMegaWarps, kMegaStageBytes, lane);
+    const uint32_t prep_bar = smem_u32(smem) + kMegaWarps * kMegaStages * kMegaStageBytes + kMegaWarps * kMegaStages * 8 + 64;
+    if (threadIdx.x == 0) {
+        mbar_init(prep_bar, 1u);
+        mbar_fence_init();
+    }
     ws.my = smem + static_cast<size_t>(warp) * kMegaStages * kMegaStageBytes;
     ws.inflight = 0;
     ws.depth = min(max(p.depth, 1), kMegaStages);
@@ -910,6 +927,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 
     const __half* x_prev = p.embed + (*p.token) * static_cast<int64_t>(p.H);
     float tw_reg = 0.f;
+    int prep_par = 0;
     int l = 0, ph = 0;  // phase: 0 q.k.v / lm_head, 1 attention, 2 o_proj, 3 router, 4 gate/up, 5 down
     const int nphases = 6 * p.layers + 1;
 
@@ -929,8 +947,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                 prefetch_l2(L.vs + kv_first, static_cast<int64_t>(kv_count) * 2);
             }
             if (ph == 2) K = A;
-            prepare_norm(p, ph == 0 ? 0 : 8, xq_s, red, ph == 0 ? x_prev : (ph == 2 ? p.attn : p.xa),
-                         ph == 0 ? L.ln1 : (ph == 2 ? nullptr : L.ln2), K, p.eps, ph == 3 ? h2f : nullptr);
+            prepare_vectors(scratch, prep_bar, prep_par, p, ph == 0 ? x_prev : (ph == 2 ? p.attn : p.xa),
+                            ph == 0 ? L.ln1 : (ph == 2 ? nullptr : L.ln2), K, 31 - __clz(K), xq_s, 0, ph == 3 ? h2f : nullptr);
+            prep_par ^= 1;
             ntasks = ph == 0 ? (last ? ws.cnt_lm : ws.cnt[KIND_A]) : (ph == 2 ? ws.cnt[KIND_C] : ws.cnt[KIND_D]);
         } else if (ph == 1) {
             AttnScratch& sm = *reinterpret_cast<AttnScratch*>(scratch);
@@ -943,7 +962,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                 route_s[lane] = tk.id;
                 route_s[32 + lane] = __float_as_int(tk.w);
             }
+            dbg_clock(p, 31);
             __syncthreads();
+            dbg_clock(p, 32);
             ws.ids_reg = route_s[lane];
             tw_reg = __int_as_float(route_s[32 + lane]);
             ws.ids_ready_layer = l;
@@ -953,7 +974,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
             }
             ntasks = ws.cnt[KIND_E];
         } else {
-            prepare_act(reinterpret_cast<uint32_t*>(scratch), p, vec_words);
+            prepare_vectors(scratch, prep_bar, prep_par, p, p.act, nullptr, p.K * p.F, 31 - __clz(p.F),
+                            reinterpret_cast<uint32_t*>(scratch), vec_words, nullptr);
+            prep_par ^= 1;
             K = p.F;
             ntasks = ws.cnt[KIND_F];
             nst = (p.K + ws.sps - 1) / ws.sps;
@@ -963,75 +986,73 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
         const int gK = K / p.group;
 
         // ---- this warp's tasks of the phase ---------------------------------------------------------------
+        // Every iteration takes one or two stages off the ring: two two-row W8 tasks at once (four rows against
+        // one read of the activation planes), one router row, or the two stages of one down row.
+        const bool rows2 = ph == 0 || ph == 2 || ph == 4;
 #pragma unroll 1
-        for (int i = 0; i < ntasks; ++i) {
-            const int task = ws.wg + i * ws.G;
-            float a0 = 0.f, a1 = 0.f;
-            bool dead = false;
+        for (int i = 0; i < ntasks; i += rows2 ? 2 : 1) {
+            const bool two = rows2 ? i + 1 < ntasks : nst > 1;
+            const unsigned char* st0 = ws.acquire();
+            const unsigned char* st1 = two ? ws.acquire_next() : st0;
+            if (!st0 || !st1) break;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            if (rows2) {
+                const __half* sc0 = reinterpret_cast<const __half*>(st0 + 2 * K);
+                const __half* sc1 = reinterpret_cast<const __half*>(st1 + 2 * K);
+                const unsigned char* const rows[4] = {st0, st0 + K, st1, st1 + K};
+                const __half* const scs[4] = {sc0, sc0 + gK, sc1, sc1 + gK};
+                dp_rows<4>(part, rows, scs, xq_s, K, lane, sbase, sstride);
+            } else if (ph == 3) {  // one fp16 router row against the fp32 h2
 #pragma unroll 1
-            for (int s = 0; s < nst; ++s) {
-                const unsigned char* st = ws.acquire();
-                if (!st) {
-                    dead = true;
-                    break;
-                }
-                if (ph == 3) {  // one fp16 router row against the fp32 h2
-#pragma unroll 1
-                    for (int c = 0; c < NCH; ++c) {
-                        const int k0 = c * 512 + lane16;
-                        if (k0 < p.H) {
-                            float hf[16];
+                for (int c = 0; c < NCH; ++c) {
+                    const int k0 = c * 512 + lane16;
+                    if (k0 < p.H) {
+                        float hf[16];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const float4 v = *reinterpret_cast<const float4*>(h2f + (((c * 4 + q) * 32 + lane) << 2));
-                                hf[4 * q] = v.x;
-                                hf[4 * q + 1] = v.y;
-                                hf[4 * q + 2] = v.z;
-                                hf[4 * q + 3] = v.w;
-                            }
-                            a0 += dot8_h(*reinterpret_cast<const uint4*>(st + 2 * k0), &hf[0]);
-                            a0 += dot8_h(*reinterpret_cast<const uint4*>(st + 2 * k0 + 16), &hf[8]);
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 v = *reinterpret_cast<const float4*>(h2f + (((c * 4 + q) * 32 + lane) << 2));
+                            hf[4 * q] = v.x;
+                            hf[4 * q + 1] = v.y;
+                            hf[4 * q + 2] = v.z;
+                            hf[4 * q + 3] = v.w;
                         }
+                        part[0] += dot8_h(*reinterpret_cast<const uint4*>(st0 + 2 * k0), &hf[0]);
+                        part[0] += dot8_h(*reinterpret_cast<const uint4*>(st0 + 2 * k0 + 16), &hf[8]);
                     }
-                } else if (ph == 5) {  // down row n of up to sps routed experts
-                    const int slot0 = s * ws.sps;
-                    const int nsl = min(ws.sps, p.K - slot0);
+                }
+            } else {  // down row n of the routed experts: sps of them per stage
 #pragma unroll 1
-                    for (int j = 0; j < nsl; ++j) {
-                        const unsigned char* const rows[1] = {st + j * p.F};
-                        const __half* const scs[1] = {reinterpret_cast<const __half*>(st + ws.sps * p.F) + j * gK};
-                        float part[1];
-                        dp_rows<1>(part, rows, scs, reinterpret_cast<const uint32_t*>(scratch) + (slot0 + j) * vec_words, p.F, lane,
-                                   sbase, sstride);
-                        a0 = fmaf(__shfl_sync(0xffffffffu, tw_reg, slot0 + j), part[0], a0);
-                    }
-                } else {  // two W8 rows of width K
-                    const __half* sc = reinterpret_cast<const __half*>(st + 2 * K);
-                    const unsigned char* const rows[2] = {st, st + K};
-                    const __half* const scs[2] = {sc, sc + gK};
-                    float part[2];
-                    dp_rows<2>(part, rows, scs, xq_s, K, lane, sbase, sstride);
-                    a0 = part[0];
-                    a1 = part[1];
+                for (int slot = 0; slot < p.K; ++slot) {
+                    const unsigned char* st = slot < ws.sps ? st0 : st1;
+                    const int j = slot < ws.sps ? slot : slot - ws.sps;
+                    const unsigned char* const rows[1] = {st + j * p.F};
+                    const __half* const scs[1] = {reinterpret_cast<const __half*>(st + ws.sps * p.F) + j * gK};
+                    float one[1];
+                    dp_rows<1>(one, rows, scs, reinterpret_cast<const uint32_t*>(scratch) + slot * vec_words, p.F, lane, sbase, sstride);
+                    part[0] = fmaf(__shfl_sync(0xffffffffu, tw_reg, slot), one[0], part[0]);
                 }
-                ws.release();
             }
-            if (dead) break;
-            a0 = warp_sum(a0);
-            a1 = warp_sum(a1);
-            if (ph == 0) {
-                if (lane < 2) (last ? p.logits : p.qkv)[task * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
-            } else if (ph == 2) {
-                if (lane < 2) {
-                    const int n = task * 2 + lane;
-                    p.xa[n] = __hadd(__float2half_rn(lane == 0 ? a0 : a1), __ldcg(x_prev + n));
+            ws.release(two ? 2 : 1);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) part[r] = warp_sum(part[r]);
+#pragma unroll 1
+            for (int t = 0; t < (rows2 && two ? 2 : 1); ++t) {
+                const int task = ws.wg + (i + t) * ws.G;
+                const float a0 = t ? part[2] : part[0], a1 = t ? part[3] : part[1];
+                if (ph == 0) {
+                    if (lane < 2) (last ? p.logits : p.qkv)[task * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
+                } else if (ph == 2) {
+                    if (lane < 2) {
+                        const int n = task * 2 + lane;
+                        p.xa[n] = __hadd(__float2half_rn(lane == 0 ? a0 : a1), __ldcg(x_prev + n));
+                    }
+                } else if (ph == 3) {
+                    if (lane == 0) p.router_logits[static_cast<int64_t>(l) * p.E + task] = __float2half_rn(a0);
+                } else if (ph == 4) {
+                    if (lane == 0) p.act[task] = __float2half_rn(a0 * (1.0f / (1.0f + expf(-a0))) * a1);
+                } else {
+                    if (lane == 0) p.xb[task] = __hadd(__float2half_rn(a0), __ldcg(p.xa + task));
                 }
-            } else if (ph == 3) {
-                if (lane == 0) p.router_logits[static_cast<int64_t>(l) * p.E + task] = __float2half_rn(a0);
-            } else if (ph == 4) {
-                if (lane == 0) p.act[task] = __float2half_rn(a0 * (1.0f / (1.0f + expf(-a0))) * a1);
-            } else {
-                if (lane == 0) p.xb[task] = __hadd(__float2half_rn(a0), __ldcg(p.xa + task));
             }
         }
         substamp(p, l, 2 * ph + 1);
@@ -1063,12 +1084,20 @@ bool mega_eligible(const lemoq_step_desc& d) {
     // one expert row of scales (gate/up rows and down rows are copied singly) must be a 16-byte multiple
     if (((d.hidden / g) * 2) % 16 != 0 || ((d.ffn / g) * 2) % 16 != 0) return false;
     if (d.ffn + 2 * (d.ffn / g) > kMegaStageBytes) return false;
+    {  // the routed experts of one down row must fit the ring: at most kMegaStages stages per task
+        int sps = kMegaStageBytes / (d.ffn + 2 * (d.ffn / g));
+        sps = sps > 4 ? 4 : sps;
+        if ((d.top_k + sps - 1) / sps > kMegaStages) return false;
+    }
     if (d.head_dim != kHeadDim || !d.kv_int8) return false;  // the fp16-KV arm runs as chained kernels
     if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
     if (d.vocab % 2 != 0 || d.layers + 1 > kMegaMaxLayers) return false;
     const size_t vec_words = 3 * (d.ffn / 16) * 4 + d.ffn / 16;
-    if (static_cast<size_t>(d.top_k) * vec_words * 4 > kMegaScratchBytes) return false;
-    if (sizeof(AttnScratch) > kMegaScratchBytes) return false;
+    if (static_cast<size_t>(d.top_k) * vec_words * 4 > kRawOff) return false;
+    auto pow2 = [](int n) { return n > 0 && (n & (n - 1)) == 0; };
+    if (!pow2(d.hidden) || !pow2(A) || !pow2(d.ffn)) return false;  // vectors are addressed by shifts
+    if (static_cast<size_t>(d.top_k) * d.ffn * 2 > kRawBytes || d.hidden * 2 > kNormWBytes || A * 2 > kNormWBytes) return false;
+    if (sizeof(AttnScratch) > kRawOff) return false;
     return true;
 }
 
