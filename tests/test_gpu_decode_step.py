@@ -148,19 +148,29 @@ def test_small_model_fp16_kv_arm(monkeypatch):
 
 @pytest.fixture
 def whole_step_kernel():
-    """Run the step engine as the single cooperative kernel (opt-in tuning key 4) for one test."""
+    """The step engine as the single cooperative kernel (the default when the shapes allow it)."""
     from lemoq import _cabi
 
     _cabi.call("lemoq_set_tuning", 4, 1)
     yield
+    _cabi.call("lemoq_set_tuning", 4, 1)
+
+
+@pytest.fixture
+def chained_kernels():
+    """The step engine as chained per-op kernels with programmatic dependent launch (tuning key 4 = 0)."""
+    from lemoq import _cabi
+
     _cabi.call("lemoq_set_tuning", 4, 0)
+    yield
+    _cabi.call("lemoq_set_tuning", 4, 1)
 
 
 def test_one_full_size_layer_whole_step_kernel(whole_step_kernel):
     _one_full_size_layer(expect_kernels=1)
 
 
-def test_one_full_size_layer_at_ctx_1024():
+def test_one_full_size_layer_chained_kernels(chained_kernels):
     _one_full_size_layer(expect_kernels=None)
 
 
@@ -216,9 +226,8 @@ def test_full_model_whole_step_kernel(whole_step_kernel):
     _full_model_greedy(1024, expect_kernels=1)
 
 
-@pytest.mark.parametrize("ctx", [1024])
-def test_full_model_32_greedy_steps_vs_oracle(ctx):
-    _full_model_greedy(ctx, expect_kernels=None)
+def test_full_model_chained_kernels(chained_kernels):
+    _full_model_greedy(1024, expect_kernels=None)
 
 
 def _full_model_greedy(ctx, expect_kernels):
