@@ -149,6 +149,25 @@ LEMOQ_API int lemoq_attn_decode_int8(const void* q, const int8_t* kc, const void
                            int num_splits, float scale, void* workspace, int* err_flag, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * lemoq_attn_decode_int8 for callers that cannot allocate: no workspace argument.
+ * This entry point has no counterpart in the reference; results equal those of
+ * lemoq_attn_decode_int8 on the same inputs.
+ * The split partials and arrival counters live in a fixed array inside the library
+ * (lemoq_attn_static_scratch_bytes() = 1 MiB per device).  The call allocates and
+ * frees nothing, and neither does anything it calls.  Sizes whose scratch need
+ * (256-byte-rounded 4*heads + 4*heads*num_splits*(D+2) bytes) exceeds the array
+ * are refused with LEMOQ_ERR_INVALID and a message in lemoq_last_error().
+ * The first call on a device looks the array's address up (once per device, with
+ * that device current); make that first call outside any stream capture.
+ * All calls on a device share the array: calls whose kernels may overlap on the
+ * device (different streams or threads) race on it - keep them on one stream.
+ */
+LEMOQ_API size_t lemoq_attn_static_scratch_bytes(void);
+LEMOQ_API int lemoq_attn_decode_int8_static(const void* q, const int8_t* kc, const void* ks, const int8_t* vc,
+                                  const void* vs, int64_t kv_head_stride, const int32_t* filled, void* out, int heads,
+                                  int S, int D, int num_splits, float scale, int* err_flag, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Router softmax + top-k: fp32 softmax over E logits, top_k rounds of arg-max
  * (lowest index wins ties), optional renormalisation.
  * ref: src/lemoq/kernels/_routing_triton.py:88 (routing_softmax_topk).

@@ -14,6 +14,8 @@
 // derives k, v) from the raw packed q.k.v projection row: RMSNorm over the full
 // projection width, head split, half-split RoPE, then writes the new K/V row into
 // the fp16 cache and the int8 mirror before attending to it.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -310,3 +312,95 @@ int launch_attn_decode(const AttnParams& p, bool int8_kv, bool fused, const Laun
 }
 
 }  // namespace lemoq
+
+// ---------------------------------------------------------------------------------------------------
+// Int8 decode attention for callers that cannot hand over a workspace.
+//
+// Some hosts of this library may not allocate device memory where they call it: a serving loop that
+// has already given every byte of the device to its own pools, a plugin that runs inside another
+// framework's stream callback or graph construction where allocation calls are forbidden, a process
+// whose memory budget was fixed at start-up.  For them the split partials and the per-head arrival
+// counters of the attention kernel live in the fixed array below, which is part of the library image:
+// nothing is allocated or freed, here or in any routine this entry point calls.
+//
+// The array holds kStaticAttnScratchBytes (1 MiB); a call whose heads x splits x (D + 2) partials plus
+// counters need more is refused with LEMOQ_ERR_INVALID.  The array starts zeroed when the module is
+// loaded (the counters must start at zero; every launch leaves them at zero again).  ALL calls on a
+// device share the one array: two calls whose kernels may run at the same time on that device (other
+// streams, other threads) race on it and give wrong results - order them on one stream.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticAttnScratchBytes = size_t(1) << 20;
+constexpr int kStaticMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
+
+// Address of the array on each device, looked up once per device with that device current.
+void* g_static_attn_ptr[kStaticMaxDevices] = {};
+std::mutex g_static_attn_mutex;
+
+int static_attn_scratch(void** out) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return lemoq::set_error(LEMOQ_ERR_CUDA, "attn_decode_int8_static: cudaGetDevice: %s", cudaGetErrorString(err));
+    if (dev < 0 || dev >= kStaticMaxDevices)
+        return lemoq::set_error(LEMOQ_ERR_UNSUPPORTED, "attn_decode_int8_static: device ordinal %d above %d", dev, kStaticMaxDevices - 1);
+    std::lock_guard<std::mutex> lock(g_static_attn_mutex);
+    if (g_static_attn_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
+        if (err != cudaSuccess || ptr == nullptr)
+            return lemoq::set_error(LEMOQ_ERR_CUDA, "attn_decode_int8_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+        g_static_attn_ptr[dev] = ptr;
+    }
+    *out = g_static_attn_ptr[dev];
+    return LEMOQ_OK;
+}
+
+}  // namespace
+
+extern "C" size_t lemoq_attn_static_scratch_bytes(void) { return kStaticAttnScratchBytes; }
+
+extern "C" int lemoq_attn_decode_int8_static(const void* q, const int8_t* kc, const void* ks, const int8_t* vc, const void* vs,
+                                             int64_t kv_head_stride, const int32_t* filled, void* out, int heads, int S, int D,
+                                             int num_splits, float scale, int* err_flag, void* stream) {
+    using namespace lemoq;
+    LEMOQ_REQUIRE(q && filled && out && kc && ks && vc && vs, LEMOQ_ERR_INVALID, "attn_decode_int8_static: null pointer");
+    LEMOQ_REQUIRE(heads > 0 && S > 0, LEMOQ_ERR_INVALID, "attn_decode_int8_static: heads and cache capacity must be positive");
+    LEMOQ_REQUIRE(D == 64 || D == 128, LEMOQ_ERR_UNSUPPORTED, "attn_decode_int8_static: head_dim=%d, built for 64 and 128", D);
+    LEMOQ_REQUIRE(num_splits >= 1 && num_splits <= 4096, LEMOQ_ERR_INVALID, "attn_decode_int8_static: num_splits must be in [1, 4096]");
+    LEMOQ_REQUIRE(aligned16(kc) && aligned16(vc) && kv_head_stride % 16 == 0, LEMOQ_ERR_INVALID,
+                  "attn_decode_int8_static: codes must be 16-byte aligned with a head stride that is a multiple of 16");
+    LEMOQ_REQUIRE(kv_head_stride >= static_cast<int64_t>(S) * D, LEMOQ_ERR_INVALID,
+                  "attn_decode_int8_static: heads overlap (head stride < S*D)");
+    // same layout as the workspace of lemoq_attn_decode_int8: counters in a 256-byte slot, then the partials
+    const size_t counters = (sizeof(unsigned int) * static_cast<size_t>(heads) + 255) / 256 * 256;
+    const size_t need = counters + sizeof(float) * static_cast<size_t>(heads) * num_splits * (D + 2);
+    LEMOQ_REQUIRE(need <= kStaticAttnScratchBytes, LEMOQ_ERR_INVALID,
+                  "attn_decode_int8_static: heads=%d x num_splits=%d x head_dim=%d needs %zu bytes of scratch, the fixed array holds %zu",
+                  heads, num_splits, D, need, kStaticAttnScratchBytes);
+    void* scratch = nullptr;
+    if (int rc = static_attn_scratch(&scratch)) return rc;
+    AttnParams p;
+    p.q = reinterpret_cast<const __half*>(q);
+    p.filled = filled;
+    p.out = reinterpret_cast<__half*>(out);
+    p.heads = heads;
+    p.S = S;
+    p.D = D;
+    p.num_splits = num_splits;
+    p.qk_scale_log2 = scale * 1.4426950408889634f;
+    p.counters = reinterpret_cast<unsigned int*>(scratch);
+    p.part = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + counters);
+    p.err_flag = err_flag;
+    p.k = kc;
+    p.v = vc;
+    p.ks = reinterpret_cast<const __half*>(ks);
+    p.vs = reinterpret_cast<const __half*>(vs);
+    p.kv_head_stride = kv_head_stride;
+    LaunchCfg lc;
+    lc.stream = static_cast<cudaStream_t>(stream);
+    return launch_attn_decode(p, true, false, lc);
+}
+

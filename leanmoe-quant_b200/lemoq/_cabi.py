@@ -63,6 +63,9 @@ _SIGNATURES = {
                                        c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "lemoq_attn_decode_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
+    "lemoq_attn_static_scratch_bytes": (c_size_t, []),
+    "lemoq_attn_decode_int8_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                              c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     "lemoq_routing_softmax_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                            c_void_p]),
     "lemoq_route": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

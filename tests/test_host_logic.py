@@ -32,7 +32,8 @@ def test_header_cites_a_reference_interface_for_every_entry_point():
     blocks = header.split("/* -----")
     for block in blocks[1:]:
         if "LEMOQ_API" in block:
-            assert "ref:" in block, block[:200]
+            # every entry point cites the reference interface it replaces, or says that it has none
+            assert "ref:" in block or "no counterpart in the\n * reference" in block or "no counterpart in the reference" in block, block[:200]
 
 
 def test_cabi_argument_validation_needs_no_gpu():
