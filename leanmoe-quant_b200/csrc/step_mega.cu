@@ -64,7 +64,8 @@ struct GridBarrier {
         __syncthreads();
         target += gridDim.x;
         if (threadIdx.x == 0) {
-            __threadfence();
+            // release at gpu scope is cumulative: it orders the writes of the whole block, which the block
+            // barrier above made visible to this thread, before the arrival
             red_release_add(counter, 1u);
             unsigned int n = 0;
             while (static_cast<int>(ld_acquire_u32(counter) - target) < 0) {
@@ -179,6 +180,43 @@ __device__ __forceinline__ void dp_rows(float (&acc)[R], const unsigned char* co
             const float sx = sxs[lc];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
+                const uint4 w = *reinterpret_cast<const uint4*>(row[r] + lc * 16);
+                int s0 = __dp4a(static_cast<int>(w.x), static_cast<int>(x0.x), 0);
+                int s1 = __dp4a(static_cast<int>(w.x), static_cast<int>(x1.x), 0);
+                int s2 = __dp4a(static_cast<int>(w.x), static_cast<int>(x2.x), 0);
+                s0 = __dp4a(static_cast<int>(w.y), static_cast<int>(x0.y), s0);
+                s1 = __dp4a(static_cast<int>(w.y), static_cast<int>(x1.y), s1);
+                s2 = __dp4a(static_cast<int>(w.y), static_cast<int>(x2.y), s2);
+                s0 = __dp4a(static_cast<int>(w.z), static_cast<int>(x0.z), s0);
+                s1 = __dp4a(static_cast<int>(w.z), static_cast<int>(x1.z), s1);
+                s2 = __dp4a(static_cast<int>(w.z), static_cast<int>(x2.z), s2);
+                s0 = __dp4a(static_cast<int>(w.w), static_cast<int>(x0.w), s0);
+                s1 = __dp4a(static_cast<int>(w.w), static_cast<int>(x1.w), s1);
+                s2 = __dp4a(static_cast<int>(w.w), static_cast<int>(x2.w), s2);
+                const float t = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
+                acc[r] = fmaf(t, sx * __half2float(sc[r][c * sstride + sbase]), acc[r]);
+            }
+        }
+    }
+}
+
+// The same for R rows that each have their OWN quantised vector (the routed experts of one down row).
+template <int R>
+__device__ __forceinline__ void dp_rows_each(float (&acc)[R], const unsigned char* const (&row)[R], const __half* const (&sc)[R],
+                                             const uint32_t* const (&xq)[R], int K, int lane, int sbase, int sstride) {
+    const int nlc = K >> 4;
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < NCH; ++c) {
+        const int lc = c * 32 + lane;
+        if (lc < nlc) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint4 x0 = *reinterpret_cast<const uint4*>(xq[r] + (0 * nlc + lc) * 4);
+                const uint4 x1 = *reinterpret_cast<const uint4*>(xq[r] + (1 * nlc + lc) * 4);
+                const uint4 x2 = *reinterpret_cast<const uint4*>(xq[r] + (2 * nlc + lc) * 4);
+                const float sx = reinterpret_cast<const float*>(xq[r] + 3 * nlc * 4)[lc];
                 const uint4 w = *reinterpret_cast<const uint4*>(row[r] + lc * 16);
                 int s0 = __dp4a(static_cast<int>(w.x), static_cast<int>(x0.x), 0);
                 int s1 = __dp4a(static_cast<int>(w.x), static_cast<int>(x1.x), 0);
@@ -423,13 +461,14 @@ struct TopK {
     int id;   // lane k: k-th expert id
     float w;  // lane k: its routing weight (fp16-rounded)
 };
+template <int PER>  // experts per lane: 2 for E <= 64, 4 for E <= 128
 __device__ __noinline__ TopK warp_topk(const __half* __restrict__ logits, int E, int K, bool norm, int lane) {
     int id_reg;
     float w_reg;
-    float v[4];
+    float v[PER];
     float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PER; ++j) {
         const int e = lane + 32 * j;
         v[j] = e < E ? __half2float(__ldcg(logits + e)) : -INFINITY;
         mx = fmaxf(mx, v[j]);
@@ -437,24 +476,27 @@ __device__ __noinline__ TopK warp_topk(const __half* __restrict__ logits, int E,
     mx = warp_max(mx);
     float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < PER; ++j) {
         const int e = lane + 32 * j;
         v[j] = e < E ? expf(v[j] - mx) : 0.f;
         sum += v[j];
     }
     sum = warp_sum(sum);
-    unsigned int key[4];  // bits of the probability + 1; 0 = absent or already taken
+    unsigned int key[PER];  // bits of the probability + 1; 0 = absent or already taken
 #pragma unroll
-    for (int j = 0; j < 4; ++j) key[j] = (lane + 32 * j) < E ? __float_as_uint(v[j] / sum) + 1u : 0u;
+    for (int j = 0; j < PER; ++j) key[j] = (lane + 32 * j) < E ? __float_as_uint(v[j] / sum) + 1u : 0u;
     float wsum = 0.f;
     id_reg = 0;
     w_reg = 0.f;
+#pragma unroll 1
     for (int k = 0; k < K; ++k) {
-        const unsigned int own = max(max(key[0], key[1]), max(key[2], key[3]));
+        unsigned int own = key[0];
+#pragma unroll
+        for (int j = 1; j < PER; ++j) own = max(own, key[j]);
         const unsigned int top = __reduce_max_sync(0xffffffffu, own);
         int bi = -1;
 #pragma unroll
-        for (int j = 3; j >= 0; --j) {
+        for (int j = PER - 1; j >= 0; --j) {
             const unsigned int b = __ballot_sync(0xffffffffu, key[j] == top);
             if (b) bi = 32 * j + __ffs(b) - 1;
         }
@@ -466,7 +508,7 @@ __device__ __noinline__ TopK warp_topk(const __half* __restrict__ logits, int E,
         }
         if ((bi & 31) == lane) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < PER; ++j)
                 if (j == (bi >> 5)) key[j] = 0u;
         }
     }
@@ -679,13 +721,15 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
     __syncthreads();
     // partial layout: acc[(h*S + split)*D + d], then the (m, l) pairs
     if (tid < D) {
+        // only the warps that had a block of positions hold anything
+        const int nactive = min(kMegaWarps, (max(ac.n_end - ac.n_start, 0) + 31) >> 5);
         float big = -INFINITY;
 #pragma unroll 1
-        for (int w = 0; w < kMegaWarps; ++w) big = fmaxf(big, sm.wm[w]);
+        for (int w = 0; w < nactive; ++w) big = fmaxf(big, sm.wm[w]);
         const float bs = big > -INFINITY ? big : 0.f;
         float a = 0.f, l = 0.f;
 #pragma unroll 1
-        for (int w = 0; w < kMegaWarps; ++w) {
+        for (int w = 0; w < nactive; ++w) {
             const float wt = exp2f(sm.wm[w] - bs);
             a = fmaf(sm.wacc[w][tid], wt, a);
             l = fmaf(sm.wl[w], wt, l);
@@ -958,7 +1002,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
             dbg_clock(p, 30);
             // one warp routes, the others pick the result up from shared memory
             if (warp == 0) {
-                const TopK tk = warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane);
+                const __half* lg = p.router_logits + static_cast<int64_t>(l) * p.E;
+                const TopK tk = p.E <= 64 ? warp_topk<2>(lg, p.E, p.K, p.norm_topk != 0, lane) : warp_topk<4>(lg, p.E, p.K, p.norm_topk != 0, lane);
                 route_s[lane] = tk.id;
                 route_s[32 + lane] = __float_as_int(tk.w);
             }
@@ -1020,16 +1065,27 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                         part[0] += dot8_h(*reinterpret_cast<const uint4*>(st0 + 2 * k0 + 16), &hf[8]);
                     }
                 }
-            } else {  // down row n of the routed experts: sps of them per stage
+            } else {  // down row n of the routed experts: sps (4) of them per stage, each against its own activations
+                const uint32_t* planes = reinterpret_cast<const uint32_t*>(scratch);
 #pragma unroll 1
-                for (int slot = 0; slot < p.K; ++slot) {
-                    const unsigned char* st = slot < ws.sps ? st0 : st1;
-                    const int j = slot < ws.sps ? slot : slot - ws.sps;
-                    const unsigned char* const rows[1] = {st + j * p.F};
-                    const __half* const scs[1] = {reinterpret_cast<const __half*>(st + ws.sps * p.F) + j * gK};
-                    float one[1];
-                    dp_rows<1>(one, rows, scs, reinterpret_cast<const uint32_t*>(scratch) + slot * vec_words, p.F, lane, sbase, sstride);
-                    part[0] = fmaf(__shfl_sync(0xffffffffu, tw_reg, slot), one[0], part[0]);
+                for (int s = 0; s < nst; ++s) {
+                    const unsigned char* st = s == 0 ? st0 : st1;
+                    const int slot0 = s * ws.sps;
+                    const __half* sc = reinterpret_cast<const __half*>(st + ws.sps * p.F);
+                    // slots past top_k (a last, partly filled stage) repeat the last valid one with weight zero
+                    const int j1 = min(1, p.K - 1 - slot0), j2 = min(2, p.K - 1 - slot0), j3 = min(3, p.K - 1 - slot0);
+                    const unsigned char* const rows[4] = {st, st + j1 * p.F, st + j2 * p.F, st + j3 * p.F};
+                    const __half* const scs[4] = {sc, sc + j1 * gK, sc + j2 * gK, sc + j3 * gK};
+                    const uint32_t* const xqs[4] = {planes + slot0 * vec_words, planes + (slot0 + j1) * vec_words,
+                                                    planes + (slot0 + j2) * vec_words, planes + (slot0 + j3) * vec_words};
+                    float one[4];
+                    dp_rows_each<4>(one, rows, scs, xqs, p.F, lane, sbase, sstride);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool valid = j < ws.sps && slot0 + j < p.K;
+                        const float tw = __shfl_sync(0xffffffffu, tw_reg, min(slot0 + j, 31));
+                        part[0] = fmaf(valid ? tw : 0.f, one[j], part[0]);
+                    }
                 }
             }
             ws.release(two ? 2 : 1);
@@ -1088,6 +1144,7 @@ bool mega_eligible(const lemoq_step_desc& d) {
         int sps = kMegaStageBytes / (d.ffn + 2 * (d.ffn / g));
         sps = sps > 4 ? 4 : sps;
         if ((d.top_k + sps - 1) / sps > kMegaStages) return false;
+        if (sps != 4 && sps < d.top_k) return false;  // the down rows are taken four routed experts at a time
     }
     if (d.head_dim != kHeadDim || !d.kv_int8) return false;  // the fp16-KV arm runs as chained kernels
     if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
