@@ -413,7 +413,7 @@ def cpu_baseline_from_session(session, model, spec_bytes, ctx: int, warmup: int)
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])

@@ -50,10 +50,17 @@ LEMOQ_API const char* lemoq_version(void);
 LEMOQ_API const char* lemoq_last_error(void);
 
 /* Kernel tuning knobs for benchmarking (process-wide, not thread-safe; defaults are the measured
- * best).  key 0: int8 dot-product mode of the streaming kernels (0 = fp32 magic-number, 1 = exact
- * fp16 codes widened to fp32, 2 = exact fp16 codes with mixed-precision FMA); key 1: warps per block
- * of the streaming kernels (1..16).  No counterpart in the reference, whose tile configs are module
- * dicts (src/lemoq/kernels/moe_grouped.py:78, src/lemoq/kernels/_dequant_triton.py:83).
+ * best).  Returns LEMOQ_ERR_INVALID for an unknown key or a value out of range.
+ *   key 0  int8 dot-product variant of the streaming GEMV kernels: 0 fp32 magic number, 1 exact fp16
+ *          codes widened to fp32, 2 exact fp16 codes with mixed-precision FMA, 3 (default) fp16 codes
+ *          with the offset folded into one correction per 16 codes
+ *   key 1  warps per block of the streaming kernels (1..16)
+ *   key 4  step engine: 1 (default) the whole-step cooperative kernel when the shapes allow it,
+ *          0 chained per-op kernels; takes effect at the next lemoq_step_create
+ *   key 5  stages a warp of the whole-step kernel keeps in flight (1..8, capped by its ring)
+ *   keys 2, 3, 6  timing experiments that skip copies or kernels: RESULTS ARE WRONG while set
+ * No counterpart in the reference, whose tile configs are module dicts
+ * (ref: src/lemoq/kernels/moe_grouped.py:78, src/lemoq/kernels/_dequant_triton.py:83).
  */
 LEMOQ_API int lemoq_set_tuning(int key, int value);
 

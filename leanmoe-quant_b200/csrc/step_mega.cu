@@ -170,7 +170,7 @@ __device__ __forceinline__ void dp_rows(float (&acc)[R], const unsigned char* co
     const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = 0.f;
-#pragma unroll 1
+#pragma unroll
     for (int c = 0; c < NCH; ++c) {
         const int lc = c * 32 + lane;
         if (lc < nlc) {
