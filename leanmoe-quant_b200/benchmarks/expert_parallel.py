@@ -1,0 +1,337 @@
+"""Batched expert-parallel decode (BASELINE config 5): B sequences in lockstep, the attention/dense part
+data-parallel over the sequences (weights replicated, every rank owns B/G sequences and their int8 KV),
+the MoE expert-parallel (expert e lives on rank e // (E/G)).
+
+Per layer and rank:  route the local tokens -> **all-to-all dispatch** of the (token, slot) pairs to the
+ranks that own their experts (fp16 activation row + global expert id, pairs sorted by expert so that a
+rank streams each resident expert's weights once) -> grouped expert GEMV on the received pairs ->
+**all-to-all combine** of the fp16 expert outputs -> routing-weighted sum at the home rank in slot order
+(fp32, one rounding) + residual.  32 all-to-alls per step over NCCL (NVLink/NVSwitch); pair counts are
+exchanged first and read on the host, so this form is not graph-capturable (a static-capacity variant
+would be).  Buffers are received into local memory before any kernel touches them; no peer pointers.
+
+There is no counterpart in the reference (its runner is batch 1, `benchmarks/runner.py`); the oracle for
+this mode is the same decoder at world size 1: results must match it token for token, which the
+dispatch/combine guarantees because every pair's expert output is computed by the same kernel on the
+same inputs whichever rank owns the expert, and the combine order is the slot order.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 --master-port P \
+        leanmoe-quant_b200/benchmarks/expert_parallel.py --sequences 64 --ctx 2048 --steps 32
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+from dataclasses import dataclass
+from typing import Any, Callable
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if _PKG not in sys.path:
+    sys.path.insert(0, _PKG)
+
+import torch  # noqa: E402
+
+
+# ---------------------------------------------------------------------------------------------------
+# dispatch / combine (device-agnostic tensor logic + torch.distributed; tested with gloo on CPU)
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class DispatchPlan:
+    order: Any          # (P,) pair indices (t*K + k) sorted by global expert id, stable
+    send_counts: list   # pairs this rank sends to each rank
+    recv_counts: list   # pairs this rank receives from each rank
+    experts_sorted: Any  # (P,) global expert ids in send order
+
+
+def owner_of(expert_ids: Any, experts_per_rank: int) -> Any:
+    return torch.div(expert_ids, experts_per_rank, rounding_mode="floor")
+
+
+def plan_dispatch(top_i: Any, *, experts: int, world: int, group: Any = None) -> DispatchPlan:
+    """``top_i (T, K)`` int64 global expert ids of the local tokens.  One count exchange (host-visible)."""
+    import torch.distributed as dist
+
+    if experts % world != 0:
+        raise ValueError("experts=%d must divide evenly over %d ranks" % (experts, world))
+    epr = experts // world
+    flat = top_i.reshape(-1)
+    if not flat.is_cuda and flat.numel() and (int(flat.min()) < 0 or int(flat.max()) >= experts):
+        raise ValueError("expert id out of range")  # (device tensors come from the routing kernel, which cannot produce one)
+    order = torch.argsort(flat, stable=True)
+    experts_sorted = flat[order]
+    send = torch.bincount(owner_of(experts_sorted, epr), minlength=world).to(torch.int64)
+    if world == 1:
+        return DispatchPlan(order, [int(send[0])], [int(send[0])], experts_sorted)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return DispatchPlan(order, [int(v) for v in send.tolist()], [int(v) for v in recv.tolist()], experts_sorted)
+
+
+def all_to_all_rows(rows: Any, send_counts: list, recv_counts: list, *, world: int, group: Any = None) -> Any:
+    """Variable-count all-to-all of the rows of ``rows`` (first dimension split by ``send_counts``)."""
+    import torch.distributed as dist
+
+    if world == 1:
+        return rows
+    out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+    return out
+
+
+def expert_parallel_moe(h: Any, top_w: Any, top_i: Any, *, experts: int, world: int, rank: int,
+                        expert_fn: Callable[[Any, Any], Any], group: Any = None) -> Any:
+    """``h (T, H)`` fp16 normalised activations, ``top_w/top_i (T, K)``.  ``expert_fn(x (R, H), local_ids (R,))
+    -> (R, H)`` fp16 runs this rank's experts on the received pairs.  Returns the fp32-combined, fp16-rounded
+    MoE output ``(T, H)`` of the local tokens."""
+    t, k = int(top_i.shape[0]), int(top_i.shape[1])
+    epr = experts // world
+    plan = plan_dispatch(top_i, experts=experts, world=world, group=group)
+    send_x = h[torch.div(plan.order, k, rounding_mode="floor")]
+    recv_x = all_to_all_rows(send_x, plan.send_counts, plan.recv_counts, world=world, group=group)
+    recv_e = all_to_all_rows(plan.experts_sorted, plan.send_counts, plan.recv_counts, world=world, group=group)
+    local_ids = recv_e - rank * epr
+    if recv_x.shape[0]:
+        # pairs arrive grouped by source rank; regroup by expert so each resident expert is streamed once
+        perm = torch.argsort(local_ids, stable=True)
+        y_sorted = expert_fn(recv_x[perm].contiguous(), local_ids[perm].contiguous())
+        y = torch.empty_like(y_sorted)
+        y[perm] = y_sorted
+    else:
+        y = recv_x.new_empty((0, h.shape[1]))
+    back = all_to_all_rows(y, plan.recv_counts, plan.send_counts, world=world, group=group)
+    pairs = torch.empty_like(back)
+    pairs[plan.order] = back  # back to (t, k) order
+    out = (pairs.reshape(t, k, -1).float() * top_w.reshape(t, k, 1).float()).sum(dim=1)
+    return out.to(h.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# the CUDA side: this rank's experts and the batched lockstep decode step
+# ---------------------------------------------------------------------------------------------------
+class LocalExperts:
+    """The W8 experts one rank owns in one layer; runs them through the grouped expert kernels."""
+
+    def __init__(self, q: Any, lo: int, hi: int) -> None:
+        self.gate_up = q.packed_gate_up[lo:hi].contiguous()
+        self.gate_up_scale = q.scale_gate_up[lo:hi].contiguous()
+        self.down = q.packed_down[lo:hi].contiguous()
+        self.down_scale = q.scale_down[lo:hi].contiguous()
+        self.group_size = int(q.group_size)
+        self.n = hi - lo
+
+    def __call__(self, x: Any, local_ids: Any) -> Any:
+        from lemoq import _cabi
+
+        _cabi.require_cuda(x, what="expert-parallel decode")
+        r, hidden = int(x.shape[0]), int(x.shape[1])
+        ffn = int(self.down.shape[2])
+        ids = local_ids.to(torch.int64).reshape(r, 1).contiguous()
+        ones = torch.ones((r, 1), dtype=torch.float16, device=x.device)
+        act = torch.empty((r, 1, ffn), dtype=torch.float16, device=x.device)
+        out = torch.empty((r, hidden), dtype=torch.float16, device=x.device)
+        stream = _cabi.current_stream(x.device)
+        _cabi.call("lemoq_moe_gate_up_w8", _cabi.ptr(x), _cabi.ptr(self.gate_up), _cabi.ptr(self.gate_up_scale), _cabi.ptr(ids),
+                   r, 1, self.n, hidden, ffn, self.group_size, _cabi.ptr(act), None, stream)
+        _cabi.call("lemoq_moe_down_w8", _cabi.ptr(act), _cabi.ptr(self.down), _cabi.ptr(self.down_scale), _cabi.ptr(ids),
+                   _cabi.ptr(ones), r, 1, self.n, hidden, ffn, self.group_size, _cabi.ptr(out), None, stream)
+        return out
+
+
+class ExpertParallelDecoder:
+    """Lockstep greedy decode of ``sequences`` sequences that share one prefilled prompt.
+
+    ``model`` is the canonical quantised module tree (after ``install_replacements``); ``session`` a batch-1
+    ``StaticCacheDecodeSession`` on it whose prefill filled the fp16 cache for the common prompt."""
+
+    def __init__(self, model: Any, session: Any, *, sequences: int, world: int, rank: int, group: Any = None,
+                 attn_splits: int = 4) -> None:
+        from lemoq import _cabi
+
+        if sequences % world != 0:
+            raise ValueError("sequences=%d must divide evenly over %d ranks" % (sequences, world))
+        cfg = model.config
+        if cfg.num_experts % world != 0:
+            raise ValueError("experts=%d must divide evenly over %d ranks" % (cfg.num_experts, world))
+        self.model, self.cfg, self.world, self.rank, self.group = model, cfg, world, rank, group
+        self.b = sequences // world
+        self.first_seq = rank * self.b
+        self.device = model.lm_head.packed.device
+        self.heads, self.dim, self.hidden = cfg.num_attention_heads, cfg.head_dim, cfg.hidden_size
+        self.max_len = int(session.config.max_cache_len)
+        self.position = int(session.position)
+        self.splits = attn_splits
+        epr = cfg.num_experts // world
+        self.local = [LocalExperts(layer.mlp._static_experts, rank * epr, (rank + 1) * epr) for layer in model.model.layers]
+        self.cos, self.sin = model.model.rotary_emb.tables(self.max_len, torch.float16, self.device)
+        # int8 KV of the shared prompt, replicated for the b local sequences: (b*heads, S, D) / (b*heads, S)
+        self.kv = []
+        stream = _cabi.current_stream(self.device)
+        for i, _ in enumerate(model.model.layers):
+            cl = session.cache.layers[i]
+            _, h, s, d = (int(v) for v in cl.keys.shape)
+            kc = torch.empty((h, s, d), dtype=torch.int8, device=self.device)
+            vc = torch.empty_like(kc)
+            ks = torch.empty((h, s), dtype=torch.float16, device=self.device)
+            vs = torch.empty_like(ks)
+            _cabi.call("lemoq_kv_int8_bulk_quantize", _cabi.ptr(cl.keys), _cabi.ptr(cl.values), _cabi.ptr(kc), _cabi.ptr(ks),
+                       _cabi.ptr(vc), _cabi.ptr(vs), h, s, d, self.position, stream)
+            self.kv.append({"kc": kc.repeat(self.b, 1, 1).contiguous(), "vc": vc.repeat(self.b, 1, 1).contiguous(),
+                            "ks": ks.repeat(self.b, 1).contiguous(), "vs": vs.repeat(self.b, 1).contiguous()})
+        ws_bytes = int(_cabi.lib().lemoq_attn_workspace_bytes(self.b * self.heads, self.dim, self.splits))
+        self.attn_ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=self.device)
+        self.pos_t = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.filled_t = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # -- one lockstep step: tokens (b,) int64 -> logits (b, V) fp16 -------------------------------------
+    def step(self, tokens: Any) -> Any:
+        from lemoq import _cabi
+        from lemoq.kernels.dequant_gemv import dequant_gemm_fused
+        from lemoq.kernels.rmsnorm import rms_norm_fused
+        from lemoq.kernels.routing import routing_softmax_topk
+
+        cfg, b, heads, dim = self.cfg, self.b, self.heads, self.dim
+        a = heads * dim
+        if self.position >= self.max_len:
+            raise RuntimeError("decode position exceeded StaticCache capacity")
+        self.pos_t.fill_(self.position)
+        self.filled_t.fill_(self.position + 1)
+        stream = _cabi.current_stream(self.device)
+        cos_row, sin_row = self.cos[self.position].contiguous(), self.sin[self.position].contiguous()
+        x = self.model.model.embed_tokens.weight[tokens]  # (b, H) fp16
+        eps = float(cfg.rms_norm_eps)
+        for i, layer in enumerate(self.model.model.layers):
+            attn, mlp = layer.self_attn, layer.mlp
+            pk = attn._lemoq_packed_qkv
+            gs = int(pk.group_size)
+            h1 = rms_norm_fused(x, layer.input_layernorm.weight, eps)
+            qkv = dequant_gemm_fused(h1, pk.packed, pk.scale, group_size=gs, out_dtype=torch.float16)  # (b, 3A)
+            q = rms_norm_fused(qkv[:, :a].contiguous(), attn.q_norm.weight, eps)
+            k = rms_norm_fused(qkv[:, a:2 * a].contiguous(), attn.k_norm.weight, eps)
+            v = qkv[:, 2 * a:].contiguous()
+            q_r, k_r = torch.empty_like(q), torch.empty_like(k)
+            # batch x heads act as heads: every sequence is at the same position
+            _cabi.call("lemoq_rope_qk", _cabi.ptr(q), dim, b * heads, _cabi.ptr(k), dim, b * heads, _cabi.ptr(cos_row),
+                       _cabi.ptr(sin_row), dim, _cabi.ptr(q_r), _cabi.ptr(k_r), stream)
+            kv = self.kv[i]
+            _cabi.call("lemoq_kv_int8_cache_write", _cabi.ptr(k_r), _cabi.ptr(v), _cabi.ptr(kv["kc"]), _cabi.ptr(kv["ks"]),
+                       _cabi.ptr(kv["vc"]), _cabi.ptr(kv["vs"]), _cabi.ptr(self.pos_t), b * heads, self.max_len, dim,
+                       _cabi.ptr(self.err), stream)
+            ctx_out = torch.empty((b, a), dtype=torch.float16, device=self.device)
+            _cabi.call("lemoq_attn_decode_int8", _cabi.ptr(q_r), _cabi.ptr(kv["kc"]), _cabi.ptr(kv["ks"]), _cabi.ptr(kv["vc"]),
+                       _cabi.ptr(kv["vs"]), self.max_len * dim, _cabi.ptr(self.filled_t), _cabi.ptr(ctx_out), b * heads,
+                       self.max_len, dim, self.splits, 1.0 / math.sqrt(dim), _cabi.ptr(self.attn_ws), _cabi.ptr(self.err), stream)
+            o = dequant_gemm_fused(ctx_out, attn.o_proj.packed, attn.o_proj.scale, group_size=gs, out_dtype=torch.float16)
+            x1 = o + x
+            h2 = rms_norm_fused(x1, layer.post_attention_layernorm.weight, eps)
+            logits = torch.matmul(h2, mlp._static_router.t())  # (b, E) fp16: a plain library GEMM
+            top_w, top_i = routing_softmax_topk(logits, top_k=cfg.num_experts_per_tok, norm_topk_prob=bool(cfg.norm_topk_prob))
+            moe = expert_parallel_moe(h2, top_w.to(torch.float16), top_i, experts=cfg.num_experts, world=self.world,
+                                      rank=self.rank, expert_fn=self.local[i], group=self.group)
+            x = moe + x1
+        hn = rms_norm_fused(x, self.model.model.norm.weight, eps)
+        lm = self.model.lm_head
+        out = dequant_gemm_fused(hn, lm.packed, lm.scale, group_size=int(lm.group_size), out_dtype=torch.float16)
+        self.position += 1
+        return out
+
+    def error_flags(self) -> int:
+        return int(self.err.item())
+
+
+def run(args: Any) -> int:
+    import torch.distributed as dist
+
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+    from benchmarks.runner import build_model, install_replacements
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = "cuda:%d" % local_rank
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    steps, ctx, seqs = args.steps, args.ctx, args.sequences
+    horizon = steps + args.warmup + 2
+    model = build_model(seed=0, device=device, layers=args.layers)
+    install_replacements(model, attn="kernel", moe="grouped", quant_cfg={"bit_width": "w8a16", "dequant": "fused", "group_size": 128},
+                         rmsnorm="fused", ctx=ctx, max_new_tokens=horizon, device=device)
+    prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
+    session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="ops")
+    dec = ExpertParallelDecoder(model, session, sequences=seqs, world=world, rank=rank)
+    # the literal configuration decodes 64 identical sequences; distinct first tokens make the exchange non-trivial
+    first = torch.arange(dec.first_seq, dec.first_seq + dec.b, device=device, dtype=torch.int64)
+    tokens = (first * 7 + 2) % model.config.vocab_size if not args.identical else torch.full_like(first, int(session.seed_token_id))
+    history = []
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        tokens = dec.step(tokens).float().argmax(dim=-1)
+        history.append(tokens.clone())
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        tokens = dec.step(tokens).float().argmax(dim=-1)
+        history.append(tokens.clone())
+    e1.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    ms = torch.tensor([max(e0.elapsed_time(e1), wall_ms)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    hist = torch.stack(history, dim=1)  # (b, warmup + steps)
+    if world > 1:
+        gathered = [torch.empty_like(hist) for _ in range(world)]
+        dist.all_gather(gathered, hist)
+        hist = torch.cat(gathered, dim=0)
+    flags = dec.error_flags()
+    if rank == 0:
+        ms_step = float(ms.item()) / steps
+        result = {"metric": "decode_tokens_per_s_batched_expert_parallel", "value": seqs * 1000.0 / ms_step, "unit": "tok/s",
+                  "n_gpus": world, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                  "scaling": "strong", "data": "synthetic",
+                  "config": {"workload": "%d sequences x ctx %d lockstep greedy decode, W8A16 + INT8 KV, experts sharded %d per GPU, "
+                                         "NCCL all-to-all dispatch/combine (BASELINE config 5)" % (seqs, ctx, model.config.num_experts // world),
+                             "layers": model.config.num_hidden_layers, "identical_sequences": bool(args.identical)},
+                  "error_flags": flags}
+        if args.check_against:
+            ref = torch.load(args.check_against)
+            result["tokens_match_reference_run"] = bool(tuple(ref.shape) == tuple(hist.shape) and torch.equal(ref, hist.cpu()))
+        print(json.dumps(result))
+        if args.tokens_out:
+            torch.save(hist.cpu(), args.tokens_out)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sequences", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--identical", action="store_true", help="all sequences start from the prompt's own next token")
+    ap.add_argument("--tokens-out", default=None, help="rank 0 saves the (sequences, warmup+steps) decoded tokens here")
+    ap.add_argument("--check-against", default=None, help="a --tokens-out file of another world size: must match token for token")
+    return run(ap.parse_args())
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
