@@ -174,13 +174,18 @@ def test_one_full_size_layer_chained_kernels(chained_kernels):
     _one_full_size_layer(expect_kernels=None)
 
 
-def _one_full_size_layer(expect_kernels):
+def test_one_full_size_layer_whole_step_kernel_ctx_4096(whole_step_kernel):
+    """BASELINE config 3's length: every warp of an attention block walks more than one block of positions."""
+    _one_full_size_layer(expect_kernels=1, ctx=4096)
+
+
+def _one_full_size_layer(expect_kernels, ctx=1024):
     """One OLMoE-sized decoder layer (hidden 2048, 16x128 heads, 64 experts top-8, ffn 1024) decoding at
     position 1024 over a seeded N(0,1) fp16 KV cache, input hidden N(0,1): logits, expert ids, KV codes."""
     from benchmarks.cudagraph import StaticCacheDecodeSession
 
     spec = glue.OlmoeSpec(layers=1, vocab=2048)
-    ctx, new = 1024, 2
+    new = 2
     wf = glue.random_float_weights(spec, seed=0, dtype=torch.float16, std=0.02)
     g = torch.Generator().manual_seed(1)
     wf.embed[7] = torch.randn(spec.hidden, generator=g).half()  # the input hidden state
