@@ -33,7 +33,7 @@
 
 namespace lemoq {
 
-constexpr int kMegaWarps = 14;
+constexpr int kMegaWarps = 16;
 constexpr int kMegaThreads = kMegaWarps * 32;
 constexpr int kMegaStages = 2;
 constexpr int kMegaStageBytes = 4224;  // 2 rows x 2048 codes + 2 x 32 bytes of scales, padded to 128
