@@ -123,11 +123,18 @@ class LocalExperts:
         self.down_scale = q.scale_down[lo:hi].contiguous()
         self.group_size = int(q.group_size)
         self.n = hi - lo
+        hidden, ffn = int(self.gate_up.shape[2]), int(self.down.shape[2])
+        self.batched = hidden % 512 == 0 and hidden <= 2048 and ffn % 512 == 0 and ffn <= 2048
 
     def __call__(self, x: Any, local_ids: Any) -> Any:
         from lemoq import _cabi
+        from lemoq.kernels.batched_w8 import w8_experts_tokens
 
         _cabi.require_cuda(x, what="expert-parallel decode")
+        if self.batched:
+            # weights-stationary kernels: every resident expert's rows are read once for all its pairs
+            return w8_experts_tokens(x, local_ids, self.gate_up, self.gate_up_scale, self.down, self.down_scale,
+                                     group_size=self.group_size)
         r, hidden = int(x.shape[0]), int(x.shape[1])
         ffn = int(self.down.shape[2])
         ids = local_ids.to(torch.int64).reshape(r, 1).contiguous()
@@ -191,8 +198,16 @@ class ExpertParallelDecoder:
     # -- one lockstep step: tokens (b,) int64 -> logits (b, V) fp16 -------------------------------------
     def step(self, tokens: Any) -> Any:
         from lemoq import _cabi
+        from lemoq.kernels.batched_w8 import w8_linear_tokens
         from lemoq.kernels.dequant_gemv import dequant_gemm_fused
         from lemoq.kernels.rmsnorm import rms_norm_fused
+
+        def linear(xin, codes, scale, gs):
+            # many tokens: the weights-stationary kernel; shapes it does not take go through the per-token GEMV
+            k = int(codes.shape[1])
+            if k % 512 == 0 and k <= 2048 and int(codes.shape[0]) % 2 == 0:
+                return w8_linear_tokens(xin, codes, scale, group_size=gs)
+            return dequant_gemm_fused(xin, codes, scale, group_size=gs, out_dtype=torch.float16)
         from lemoq.kernels.routing import routing_softmax_topk
 
         cfg, b, heads, dim = self.cfg, self.b, self.heads, self.dim
@@ -210,7 +225,7 @@ class ExpertParallelDecoder:
             pk = attn._lemoq_packed_qkv
             gs = int(pk.group_size)
             h1 = rms_norm_fused(x, layer.input_layernorm.weight, eps)
-            qkv = dequant_gemm_fused(h1, pk.packed, pk.scale, group_size=gs, out_dtype=torch.float16)  # (b, 3A)
+            qkv = linear(h1, pk.packed, pk.scale, gs)  # (b, 3A)
             q = rms_norm_fused(qkv[:, :a].contiguous(), attn.q_norm.weight, eps)
             k = rms_norm_fused(qkv[:, a:2 * a].contiguous(), attn.k_norm.weight, eps)
             v = qkv[:, 2 * a:].contiguous()
@@ -226,7 +241,7 @@ class ExpertParallelDecoder:
             _cabi.call("lemoq_attn_decode_int8", _cabi.ptr(q_r), _cabi.ptr(kv["kc"]), _cabi.ptr(kv["ks"]), _cabi.ptr(kv["vc"]),
                        _cabi.ptr(kv["vs"]), self.max_len * dim, _cabi.ptr(self.filled_t), _cabi.ptr(ctx_out), b * heads,
                        self.max_len, dim, self.splits, 1.0 / math.sqrt(dim), _cabi.ptr(self.attn_ws), _cabi.ptr(self.err), stream)
-            o = dequant_gemm_fused(ctx_out, attn.o_proj.packed, attn.o_proj.scale, group_size=gs, out_dtype=torch.float16)
+            o = linear(ctx_out, attn.o_proj.packed, attn.o_proj.scale, gs)
             x1 = o + x
             h2 = rms_norm_fused(x1, layer.post_attention_layernorm.weight, eps)
             logits = torch.matmul(h2, mlp._static_router.t())  # (b, E) fp16: a plain library GEMM
@@ -236,7 +251,7 @@ class ExpertParallelDecoder:
             x = moe + x1
         hn = rms_norm_fused(x, self.model.model.norm.weight, eps)
         lm = self.model.lm_head
-        out = dequant_gemm_fused(hn, lm.packed, lm.scale, group_size=int(lm.group_size), out_dtype=torch.float16)
+        out = linear(hn, lm.packed, lm.scale, int(lm.group_size))
         self.position += 1
         return out
 

@@ -18,12 +18,17 @@
 //
 // Phases per layer (all blocks take part in each):
 //   A  q.k.v rows          x = RMSNorm(x_prev)                                   -> qkv
-//   B  attention           one (head, split) per block; fused q/k norm + RoPE + KV write   -> partials
-//   C  o_proj rows         every block merges the attention partials itself; + residual -> x1
-//   D  router rows (fp16)  h2 = RMSNorm(x1) (kept in shared memory for E)        -> router logits
-//   E  expert gate/up      every warp derives the top-k itself from the logits; SwiGLU -> act
+//   B  attention           one (head, split) per block; fused q/k norm + RoPE + KV write; the block that
+//                          arrives last at a head's counter merges the head's splits   -> attn
+//   C  o_proj rows         + residual                                             -> x1
+//   D  router rows (fp16)  h2 = RMSNorm(x1) (its planes stay in shared memory for E) -> router logits
+//   E  expert gate/up      one warp per block derives the top-k from the logits; SwiGLU -> act
 //   F  expert down         routing-weighted sum + residual                        -> x2
-// then the lm_head rows on RMSNorm(x2).
+// then the lm_head rows on RMSNorm(x2), streamed as the q.k.v rows of a pseudo layer.
+//
+// The per-layer code runs once per layer, so it is cold in the first-level instruction cache every time:
+// cold loops are rolled and the phases share one task loop, one activation-prep routine and one refill
+// site on purpose (code size showed up directly in the step time).
 #include <cstddef>
 #include <cstdio>
 #include <cstdlib>

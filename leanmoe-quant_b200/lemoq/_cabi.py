@@ -63,6 +63,10 @@ _SIGNATURES = {
                                        c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "lemoq_attn_decode_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
+    "lemoq_w8_token_planes_bytes": (c_size_t, [c_int, c_int]),
+    "lemoq_w8_quantise_tokens": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "lemoq_w8_rows_tokens": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                     c_void_p, c_void_p]),
     "lemoq_attn_static_scratch_bytes": (c_size_t, []),
     "lemoq_attn_decode_int8_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),

@@ -1,0 +1,60 @@
+"""W8 linears and grouped experts for MANY tokens per call (batched decode): weights-stationary kernels,
+every weight byte read once per call.  The reference's T > 1 arms dequantise and call a dense matmul
+(`quant/linear.py:365`, `moe_static.py:329`); these compute the same sums with exact integer partial sums.
+CUDA only: there is no CPU path."""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from lemoq import _cabi
+
+
+def quantise_tokens(x: Any) -> Any:
+    """``x (T, K)`` fp16 contiguous -> opaque digit-plane buffer for :func:`w8_rows_tokens`."""
+    if x.dim() != 2 or x.dtype != torch.float16 or not x.is_contiguous():
+        raise ValueError("x 必须是连续的 (T, K) fp16")
+    _cabi.require_cuda(x, what="batched W8 kernels")
+    t, k = int(x.shape[0]), int(x.shape[1])
+    planes = torch.empty(max(int(_cabi.lib().lemoq_w8_token_planes_bytes(max(t, 1), k)), 16), dtype=torch.uint8, device=x.device)
+    _cabi.call("lemoq_w8_quantise_tokens", _cabi.ptr(x), t, k, _cabi.ptr(planes), _cabi.current_stream(x.device))
+    return planes
+
+
+def w8_rows_tokens(planes: Any, tokens: int, codes: Any, scale: Any, *, group_size: int, seg_offsets: Any = None,
+                   gate_up: bool = False) -> Any:
+    """``codes (N, K)`` or ``(E, N, K)`` int8, ``scale`` matching fp16 -> ``(T, N)`` fp16, or ``(T, N/2)`` =
+    silu(gate) * up when ``gate_up``.  ``seg_offsets (E+1,)`` int32: tokens ``[seg[e], seg[e+1])`` use expert e."""
+    if codes.dtype != torch.int8 or scale.dtype != torch.float16:
+        raise ValueError("codes 必须 int8，scale 必须 fp16")
+    if not (codes.is_contiguous() and scale.is_contiguous()):
+        raise ValueError("codes/scale 必须连续")
+    e = int(codes.shape[0]) if codes.dim() == 3 else 1
+    n, k = int(codes.shape[-2]), int(codes.shape[-1])
+    if e > 1 and (seg_offsets is None or seg_offsets.dtype != torch.int32 or int(seg_offsets.numel()) != e + 1):
+        raise ValueError("多专家调用需要 (E+1,) int32 的 seg_offsets")
+    out = torch.empty((tokens, n // 2 if gate_up else n), dtype=torch.float16, device=codes.device)
+    _cabi.call("lemoq_w8_rows_tokens", _cabi.ptr(planes), tokens, _cabi.ptr(codes), _cabi.ptr(scale), n, k, int(group_size),
+               _cabi.ptr(seg_offsets) if seg_offsets is not None else None, e, 1 if gate_up else 0, _cabi.ptr(out),
+               _cabi.current_stream(codes.device))
+    return out
+
+
+def w8_linear_tokens(x: Any, codes: Any, scale: Any, *, group_size: int) -> Any:
+    """``x (T, K)`` fp16 -> ``(T, N)`` fp16 through a W8 linear ``codes (N, K)``."""
+    return w8_rows_tokens(quantise_tokens(x.contiguous()), int(x.shape[0]), codes, scale, group_size=group_size)
+
+
+def w8_experts_tokens(x: Any, expert_ids: Any, gate_up: Any, gate_up_scale: Any, down: Any, down_scale: Any, *,
+                      group_size: int) -> Any:
+    """Grouped experts on pairs SORTED by expert: ``x (R, H)`` fp16, ``expert_ids (R,)`` ascending local ids ->
+    ``(R, H)`` fp16 unweighted expert outputs (gate/up + SwiGLU, then down)."""
+    r = int(x.shape[0])
+    e = int(gate_up.shape[0])
+    counts = torch.bincount(expert_ids, minlength=e)
+    seg = torch.zeros(e + 1, dtype=torch.int32, device=x.device)
+    seg[1:] = torch.cumsum(counts, dim=0).to(torch.int32)
+    act = w8_rows_tokens(quantise_tokens(x.contiguous()), r, gate_up, gate_up_scale, group_size=group_size, seg_offsets=seg, gate_up=True)
+    return w8_rows_tokens(quantise_tokens(act), r, down, down_scale, group_size=group_size, seg_offsets=seg)
