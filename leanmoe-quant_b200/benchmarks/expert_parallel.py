@@ -110,6 +110,51 @@ def expert_parallel_moe(h: Any, top_w: Any, top_i: Any, *, experts: int, world: 
     return out.to(h.dtype)
 
 
+def expert_parallel_moe_static(h: Any, top_w: Any, top_i: Any, *, experts: int, world: int, rank: int,
+                               expert_fn: Callable[[Any, Any], Any], group: Any = None) -> Any:
+    """The same exchange with a STATIC capacity: every rank sends every peer a buffer of T*K pair slots (the
+    worst case), unused slots carry the expert id ``experts`` and are sorted behind the real pairs, where
+    ``expert_fn`` must ignore them.  No tensor shape and no collective size depends on the routing and nothing
+    is read on the host, so the whole step can be captured in a CUDA graph.  Same results as
+    :func:`expert_parallel_moe` bit for bit: every real pair meets the same kernel with the same inputs."""
+    import torch.distributed as dist
+
+    t, k = int(top_i.shape[0]), int(top_i.shape[1])
+    pairs_n, hidden, epr, dev = t * k, int(h.shape[1]), experts // world, h.device
+    flat = top_i.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    sorted_e = flat[order]
+    dest = torch.div(sorted_e, epr, rounding_mode="floor")
+    counts = (dest.reshape(-1, 1) == torch.arange(world, device=dev).reshape(1, -1)).sum(dim=0)
+    starts = torch.cumsum(counts, dim=0) - counts
+    pos = torch.arange(pairs_n, device=dev) - starts[dest]
+    send_x = h.new_zeros((world, pairs_n, hidden))
+    send_e = torch.full((world, pairs_n), experts, dtype=torch.int64, device=dev)
+    send_x[dest, pos] = h[torch.div(order, k, rounding_mode="floor")]
+    send_e[dest, pos] = sorted_e
+    if world > 1:
+        recv_x, recv_e = torch.empty_like(send_x), torch.empty_like(send_e)
+        dist.all_to_all_single(recv_x, send_x, group=group)
+        dist.all_to_all_single(recv_e, send_e, group=group)
+    else:
+        recv_x, recv_e = send_x, send_e
+    local = torch.where(recv_e == experts, torch.full_like(recv_e, epr), recv_e - rank * epr).reshape(-1)
+    perm = torch.argsort(local, stable=True)
+    y_sorted = expert_fn(recv_x.reshape(-1, hidden)[perm].contiguous(), local[perm].contiguous())
+    y = torch.empty_like(y_sorted)
+    y[perm] = y_sorted
+    y = y.reshape(world, pairs_n, hidden)
+    if world > 1:
+        back = torch.empty_like(y)
+        dist.all_to_all_single(back, y, group=group)
+    else:
+        back = y
+    pairs = torch.empty((pairs_n, hidden), dtype=h.dtype, device=dev)
+    pairs[order] = back[dest, pos]
+    out = (pairs.reshape(t, k, -1).float() * top_w.reshape(t, k, 1).float()).sum(dim=1)
+    return out.to(h.dtype)
+
+
 # ---------------------------------------------------------------------------------------------------
 # the CUDA side: this rank's experts and the batched lockstep decode step
 # ---------------------------------------------------------------------------------------------------
@@ -156,7 +201,7 @@ class ExpertParallelDecoder:
     ``StaticCacheDecodeSession`` on it whose prefill filled the fp16 cache for the common prompt."""
 
     def __init__(self, model: Any, session: Any, *, sequences: int, world: int, rank: int, group: Any = None,
-                 attn_splits: int = 4) -> None:
+                 attn_splits: int = 4, static_exchange: bool = False) -> None:
         from lemoq import _cabi
 
         if sequences % world != 0:
@@ -172,8 +217,12 @@ class ExpertParallelDecoder:
         self.max_len = int(session.config.max_cache_len)
         self.position = int(session.position)
         self.splits = attn_splits
+        self.static_exchange = static_exchange
+        self.graph = None
         epr = cfg.num_experts // world
         self.local = [LocalExperts(layer.mlp._static_experts, rank * epr, (rank + 1) * epr) for layer in model.model.layers]
+        if static_exchange and not all(le.batched for le in self.local):
+            raise NotImplementedError("the static-capacity exchange needs the many-token expert kernels (widths % 512 == 0, <= 2048)")
         self.cos, self.sin = model.model.rotary_emb.tables(self.max_len, torch.float16, self.device)
         # int8 KV of the shared prompt, replicated for the b local sequences: (b*heads, S, D) / (b*heads, S)
         self.kv = []
@@ -197,6 +246,40 @@ class ExpertParallelDecoder:
 
     # -- one lockstep step: tokens (b,) int64 -> logits (b, V) fp16 -------------------------------------
     def step(self, tokens: Any) -> Any:
+        if self.position >= self.max_len:
+            raise RuntimeError("decode position exceeded StaticCache capacity")
+        self.pos_t.fill_(self.position)
+        self.filled_t.fill_(self.position + 1)
+        if self.graph is not None:
+            self.static_tokens.copy_(tokens)
+            self.graph.replay()
+            out = self.static_logits
+        else:
+            out = self._forward(tokens)
+        self.position += 1
+        return out
+
+    def capture(self, warmup: int = 2) -> None:
+        """Capture the step (exchange included) in one CUDA graph; needs the static-capacity exchange.  The warm-up
+        steps run eagerly at the current position and are undone (the position does not advance)."""
+        if not self.static_exchange:
+            raise RuntimeError("graph capture needs static_exchange=True (the dynamic exchange reads counts on the host)")
+        self.static_tokens = torch.zeros(self.b, dtype=torch.int64, device=self.device)
+        self.pos_t.fill_(self.position)
+        self.filled_t.fill_(self.position + 1)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._forward(self.static_tokens)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.static_logits = self._forward(self.static_tokens)
+        self.graph = graph
+
+    def _forward(self, tokens: Any) -> Any:
         from lemoq import _cabi
         from lemoq.kernels.batched_w8 import w8_linear_tokens
         from lemoq.kernels.dequant_gemv import dequant_gemm_fused
@@ -212,12 +295,11 @@ class ExpertParallelDecoder:
 
         cfg, b, heads, dim = self.cfg, self.b, self.heads, self.dim
         a = heads * dim
-        if self.position >= self.max_len:
-            raise RuntimeError("decode position exceeded StaticCache capacity")
-        self.pos_t.fill_(self.position)
-        self.filled_t.fill_(self.position + 1)
         stream = _cabi.current_stream(self.device)
-        cos_row, sin_row = self.cos[self.position].contiguous(), self.sin[self.position].contiguous()
+        # the position lives in device scalars (pos_t / filled_t) so that a captured graph follows it
+        cos_row = self.cos.index_select(0, self.pos_t).reshape(-1).contiguous()
+        sin_row = self.sin.index_select(0, self.pos_t).reshape(-1).contiguous()
+        moe_fn = expert_parallel_moe_static if self.static_exchange else expert_parallel_moe
         x = self.model.model.embed_tokens.weight[tokens]  # (b, H) fp16
         eps = float(cfg.rms_norm_eps)
         for i, layer in enumerate(self.model.model.layers):
@@ -246,14 +328,12 @@ class ExpertParallelDecoder:
             h2 = rms_norm_fused(x1, layer.post_attention_layernorm.weight, eps)
             logits = torch.matmul(h2, mlp._static_router.t())  # (b, E) fp16: a plain library GEMM
             top_w, top_i = routing_softmax_topk(logits, top_k=cfg.num_experts_per_tok, norm_topk_prob=bool(cfg.norm_topk_prob))
-            moe = expert_parallel_moe(h2, top_w.to(torch.float16), top_i, experts=cfg.num_experts, world=self.world,
-                                      rank=self.rank, expert_fn=self.local[i], group=self.group)
+            moe = moe_fn(h2, top_w.to(torch.float16), top_i, experts=cfg.num_experts, world=self.world,
+                         rank=self.rank, expert_fn=self.local[i], group=self.group)
             x = moe + x1
         hn = rms_norm_fused(x, self.model.model.norm.weight, eps)
         lm = self.model.lm_head
-        out = linear(hn, lm.packed, lm.scale, int(lm.group_size))
-        self.position += 1
-        return out
+        return linear(hn, lm.packed, lm.scale, int(lm.group_size))
 
     def error_flags(self) -> int:
         return int(self.err.item())
@@ -279,7 +359,9 @@ def run(args: Any) -> int:
                          rmsnorm="fused", ctx=ctx, max_new_tokens=horizon, device=device)
     prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
     session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="ops")
-    dec = ExpertParallelDecoder(model, session, sequences=seqs, world=world, rank=rank)
+    dec = ExpertParallelDecoder(model, session, sequences=seqs, world=world, rank=rank, static_exchange=args.exchange == "static")
+    if args.graph:
+        dec.capture()
     # the literal configuration decodes 64 identical sequences; distinct first tokens make the exchange non-trivial
     first = torch.arange(dec.first_seq, dec.first_seq + dec.b, device=device, dtype=torch.int64)
     tokens = (first * 7 + 2) % model.config.vocab_size if not args.identical else torch.full_like(first, int(session.seed_token_id))
@@ -321,7 +403,8 @@ def run(args: Any) -> int:
                   "scaling": "strong", "data": "synthetic",
                   "config": {"workload": "%d sequences x ctx %d lockstep greedy decode, W8A16 + INT8 KV, experts sharded %d per GPU, "
                                          "NCCL all-to-all dispatch/combine (BASELINE config 5)" % (seqs, ctx, model.config.num_experts // world),
-                             "layers": model.config.num_hidden_layers, "identical_sequences": bool(args.identical)},
+                             "layers": model.config.num_hidden_layers, "identical_sequences": bool(args.identical),
+                             "exchange": args.exchange, "cuda_graph": bool(args.graph)},
                   "error_flags": flags}
         if args.check_against:
             ref = torch.load(args.check_against)
@@ -342,6 +425,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--exchange", default="static", choices=["static", "dynamic"],
+                    help="static: fixed-capacity all-to-all, nothing read on the host; dynamic: counts exchanged and read per layer")
+    ap.add_argument("--graph", action="store_true", help="capture the step (with its all-to-alls) in one CUDA graph; static exchange only")
     ap.add_argument("--identical", action="store_true", help="all sequences start from the prompt's own next token")
     ap.add_argument("--tokens-out", default=None, help="rank 0 saves the (sequences, warmup+steps) decoded tokens here")
     ap.add_argument("--check-against", default=None, help="a --tokens-out file of another world size: must match token for token")

@@ -77,7 +77,40 @@ struct TokParams {
     int T, N, K, group, E, gate_up;
 };
 
-// grid = (ceil(row pairs / kRowWarps), E); dynamic smem = kTokTile * plane_words(K) * 4 bytes
+// Sixteen per-lane partial sums -> sixteen warp totals with 16 shuffles: every round halves the values a
+// lane carries and doubles the lanes that agree.  Afterwards lane L holds the total of value
+// ((L>>4)&1)*8 + ((L>>3)&1)*4 + ((L>>2)&1)*2 + ((L>>1)&1) (both lanes of an even/odd pair hold the same).
+__device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const bool up = (lane & 16) != 0;
+        const float keep = up ? v[i + 8] : v[i], give = up ? v[i] : v[i + 8];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const bool up = (lane & 8) != 0;
+        const float keep = up ? v[i + 4] : v[i], give = up ? v[i] : v[i + 4];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const bool up = (lane & 4) != 0;
+        const float keep = up ? v[i + 2] : v[i], give = up ? v[i] : v[i + 2];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
+    {
+        const bool up = (lane & 2) != 0;
+        const float keep = up ? v[1] : v[0], give = up ? v[0] : v[1];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, give, 2);
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
+
+// grid = (ceil(row pairs / kRowWarps), E); dynamic smem = kTokTile * plane_words(K) * 4 bytes.
+// One row pair per warp: its weights stay in registers while the warp walks all token tiles of the segment.
+// (A variant that kept the token tile and walked eight row pairs per warp was slower for the experts: the
+// serial weight loads of a warp are not hidden, thousands of small blocks hide them better.)
 template <int NCH>
 __global__ void __launch_bounds__(kRowWarps * 32) w8_tokens_kernel(const TokParams p) {
     extern __shared__ __align__(16) uint32_t tile[];
@@ -86,77 +119,92 @@ __global__ void __launch_bounds__(kRowWarps * 32) w8_tokens_kernel(const TokPara
     const int t0 = p.seg ? p.seg[e] : 0, t1 = p.seg ? p.seg[e + 1] : p.T;
     if (t1 <= t0) return;
     const int pairs = p.N / 2;
-    const int pair = blockIdx.x * kRowWarps + warp;
-    const bool live = pair < pairs;
-    // rows of this warp: (2i, 2i+1), or (n, N/2 + n) when the gate and the up row meet in the SwiGLU epilogue
-    const int r0 = p.gate_up ? pair : 2 * pair, r1 = p.gate_up ? pairs + pair : 2 * pair + 1;
     const int nlc = p.K / 16, gK = p.K / p.group, pw = plane_words(p.K);
     const int64_t base = static_cast<int64_t>(e) * p.N;
     uint4 w[2][NCH];
     float sc[2][NCH];
+    auto load_rows = [&](int pair) {
+        // rows of the pair: (2i, 2i+1), or (n, N/2 + n) when the gate and the up row meet in the SwiGLU epilogue
+        const int r0 = p.gate_up ? pair : 2 * pair, r1 = p.gate_up ? pairs + pair : 2 * pair + 1;
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) {
-        const int lc = c * 32 + lane;
-        const bool on = live && lc < nlc;
+        for (int c = 0; c < NCH; ++c) {
+            const int lc = c * 32 + lane;
+            const bool on = pair < pairs && lc < nlc;
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const int64_t row = base + (r == 0 ? r0 : r1);
-            w[r][c] = on ? ld_stream16(p.codes + row * p.K + lc * 16) : make_uint4(0, 0, 0, 0);
-            sc[r][c] = on ? __half2float(p.scale[row * gK + (lc * 16) / p.group]) : 0.f;
+            for (int r = 0; r < 2; ++r) {
+                const int64_t row = base + (r == 0 ? r0 : r1);
+                w[r][c] = on ? ld_stream16(p.codes + row * p.K + lc * 16) : make_uint4(0, 0, 0, 0);
+                sc[r][c] = on ? __half2float(p.scale[row * gK + (lc * 16) / p.group]) : 0.f;
+            }
         }
-    }
-    for (int tb = t0; tb < t1; tb += kTokTile) {
-        const int nt = min(kTokTile, t1 - tb);
+    };
+    auto stage_tile = [&](int tb, int nt) {
         __syncthreads();  // the previous tile has been consumed
-        {
-            const uint4* src = reinterpret_cast<const uint4*>(p.planes + static_cast<int64_t>(tb) * pw);
-            uint4* dst = reinterpret_cast<uint4*>(tile);
-            for (int i = threadIdx.x; i < nt * pw / 4; i += blockDim.x) dst[i] = __ldg(src + i);
-        }
+        const uint4* src = reinterpret_cast<const uint4*>(p.planes + static_cast<int64_t>(tb) * pw);
+        uint4* dst = reinterpret_cast<uint4*>(tile);
+        for (int i = threadIdx.x; i < nt * pw / 4; i += blockDim.x) dst[i] = __ldg(src + i);
         __syncthreads();
-        if (!live) continue;
-        for (int tt = 0; tt < nt; ++tt) {
-            const uint32_t* xq = tile + tt * pw;
-            const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
-            float a0 = 0.f, a1 = 0.f;
+    };
+    auto compute_tile = [&](int pair, int tb, int nt) {
+        float acc[16];  // [token][row]
 #pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-                const int lc = c * 32 + lane;
-                if (lc < nlc) {
-                    const uint4 x0 = *reinterpret_cast<const uint4*>(xq + (0 * nlc + lc) * 4);
-                    const uint4 x1 = *reinterpret_cast<const uint4*>(xq + (1 * nlc + lc) * 4);
-                    const uint4 x2 = *reinterpret_cast<const uint4*>(xq + (2 * nlc + lc) * 4);
-                    const float sx = sxs[lc];
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        const uint4 ww = w[r][c];
-                        int s0 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x0.x), 0);
-                        int s1 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x1.x), 0);
-                        int s2 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x2.x), 0);
-                        s0 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x0.y), s0);
-                        s1 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x1.y), s1);
-                        s2 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x2.y), s2);
-                        s0 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x0.z), s0);
-                        s1 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x1.z), s1);
-                        s2 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x2.z), s2);
-                        s0 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x0.w), s0);
-                        s1 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x1.w), s1);
-                        s2 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x2.w), s2);
-                        const float tsum = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
-                        if (r == 0) a0 = fmaf(tsum, sx * sc[0][c], a0);
-                        else a1 = fmaf(tsum, sx * sc[1][c], a1);
+        for (int tt = 0; tt < kTokTile; ++tt) {
+            if (tt < nt) {
+                const uint32_t* xq = tile + tt * pw;
+                const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    const int lc = c * 32 + lane;
+                    if (lc < nlc) {
+                        const uint4 x0 = *reinterpret_cast<const uint4*>(xq + (0 * nlc + lc) * 4);
+                        const uint4 x1 = *reinterpret_cast<const uint4*>(xq + (1 * nlc + lc) * 4);
+                        const uint4 x2 = *reinterpret_cast<const uint4*>(xq + (2 * nlc + lc) * 4);
+                        const float sx = sxs[lc];
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const uint4 ww = w[r][c];
+                            int s0 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x0.x), 0);
+                            int s1 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x1.x), 0);
+                            int s2 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x2.x), 0);
+                            s0 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x0.y), s0);
+                            s1 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x1.y), s1);
+                            s2 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x2.y), s2);
+                            s0 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x0.z), s0);
+                            s1 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x1.z), s1);
+                            s2 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x2.z), s2);
+                            s0 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x0.w), s0);
+                            s1 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x1.w), s1);
+                            s2 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x2.w), s2);
+                            const float tsum = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
+                            acc[2 * tt + r] = fmaf(tsum, sx * sc[r][c], acc[2 * tt + r]);
+                        }
                     }
                 }
             }
-            a0 = warp_sum(a0);
-            a1 = warp_sum(a1);
+        }
+        const float total = warp_reduce16(acc, lane);
+        // this lane's value: token tt, row r
+        const int idx = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+        const int tt = idx >> 1, r = idx & 1;
+        // gate (r = 0) and up (r = 1) of one token sit in lanes that differ in bit 1 (every lane takes part)
+        const float other = __shfl_xor_sync(0xffffffffu, total, 2);
+        if (pair < pairs && tt < nt && (lane & 1) == 0) {
             const int64_t tok = tb + tt;
             if (p.gate_up) {
-                if (lane == 0) p.y[tok * pairs + pair] = __float2half_rn(a0 * (1.0f / (1.0f + expf(-a0))) * a1);
-            } else if (lane < 2) {
-                p.y[tok * p.N + (lane == 0 ? r0 : r1)] = __float2half_rn(lane == 0 ? a0 : a1);
+                if (r == 0) p.y[tok * pairs + pair] = __float2half_rn(total * (1.0f / (1.0f + expf(-total))) * other);
+            } else {
+                p.y[tok * p.N + (r == 0 ? 2 * pair : 2 * pair + 1)] = __float2half_rn(total);
             }
         }
+    };
+    const int pair = blockIdx.x * kRowWarps + warp;
+    load_rows(pair);
+    for (int tb = t0; tb < t1; tb += kTokTile) {
+        const int nt = min(kTokTile, t1 - tb);
+        stage_tile(tb, nt);
+        compute_tile(pair, tb, nt);
     }
 }
 

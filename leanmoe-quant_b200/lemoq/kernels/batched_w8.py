@@ -50,10 +50,13 @@ def w8_linear_tokens(x: Any, codes: Any, scale: Any, *, group_size: int) -> Any:
 def w8_experts_tokens(x: Any, expert_ids: Any, gate_up: Any, gate_up_scale: Any, down: Any, down_scale: Any, *,
                       group_size: int) -> Any:
     """Grouped experts on pairs SORTED by expert: ``x (R, H)`` fp16, ``expert_ids (R,)`` ascending local ids ->
-    ``(R, H)`` fp16 unweighted expert outputs (gate/up + SwiGLU, then down)."""
+    ``(R, H)`` fp16 unweighted expert outputs (gate/up + SwiGLU, then down).  Rows whose id is >= the number of
+    experts (padding of a static-capacity exchange) must come last; their outputs are left unwritten."""
     r = int(x.shape[0])
     e = int(gate_up.shape[0])
-    counts = torch.bincount(expert_ids, minlength=e)
+    # counts without a data-dependent shape (no host sync: usable under stream capture); ids >= e (padding rows
+    # sorted behind the real ones) belong to no segment and are never touched
+    counts = (expert_ids.reshape(-1, 1) == torch.arange(e, device=x.device).reshape(1, -1)).sum(dim=0)
     seg = torch.zeros(e + 1, dtype=torch.int32, device=x.device)
     seg[1:] = torch.cumsum(counts, dim=0).to(torch.int32)
     act = w8_rows_tokens(quantise_tokens(x.contiguous()), r, gate_up, gate_up_scale, group_size=group_size, seg_offsets=seg, gate_up=True)

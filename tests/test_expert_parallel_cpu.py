@@ -40,23 +40,30 @@ def _expected(h, top_w, top_i):
     return (pairs.float() * top_w.reshape(t, k, 1).float()).sum(dim=1).half()
 
 
-def _worker(rank, world, port, tokens, failures):
+def _worker(rank, world, port, tokens, static, failures):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from benchmarks.expert_parallel import expert_parallel_moe, plan_dispatch
+        from benchmarks.expert_parallel import expert_parallel_moe, expert_parallel_moe_static, plan_dispatch
 
         epr = EXPERTS // world
         h, top_w, top_i = _inputs(rank, tokens)
         seen = []
 
         def expert_fn(x, local_ids):
-            assert int(local_ids.min()) >= 0 and int(local_ids.max()) < epr  # only experts this rank owns arrive
             assert torch.equal(local_ids, torch.sort(local_ids).values)       # grouped by expert
             seen.append(int(x.shape[0]))
+            if static:
+                # padding slots carry the id `epr` behind the real pairs; their outputs must never be used
+                assert int(local_ids.min()) >= 0 and int(local_ids.max()) <= epr and x.shape[0] == world * tokens * TOP_K
+                y = _fake_expert(x, local_ids + rank * epr)
+                y[local_ids == epr] = float("nan")
+                return y
+            assert int(local_ids.min()) >= 0 and int(local_ids.max()) < epr  # only experts this rank owns arrive
             return _fake_expert(x, local_ids + rank * epr)
 
-        out = expert_parallel_moe(h, top_w, top_i, experts=EXPERTS, world=world, rank=rank, expert_fn=expert_fn)
+        moe = expert_parallel_moe_static if static else expert_parallel_moe
+        out = moe(h, top_w, top_i, experts=EXPERTS, world=world, rank=rank, expert_fn=expert_fn)
         if not torch.equal(out, _expected(h, top_w, top_i)):
             failures.put((rank, "combined output differs from the exchange-free result"))
         plan = plan_dispatch(top_i, experts=EXPERTS, world=world)
@@ -78,12 +85,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 5), (1, 4)])
-def test_dispatch_combine_matches_exchange_free_result(world, tokens):
+@pytest.mark.parametrize("world,tokens,static", [(2, 5, False), (1, 4, False), (2, 5, True), (1, 4, True)])
+def test_dispatch_combine_matches_exchange_free_result(world, tokens, static):
     ctx = mp.get_context("spawn")
     failures = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, tokens, failures)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, tokens, static, failures)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
