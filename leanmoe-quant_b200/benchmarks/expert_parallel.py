@@ -275,7 +275,8 @@ class ExpertParallelDecoder:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread_local: the process group's watchdog thread may call CUDA while this thread captures
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self.static_logits = self._forward(self.static_tokens)
         self.graph = graph
 
@@ -362,6 +363,8 @@ def run(args: Any) -> int:
     dec = ExpertParallelDecoder(model, session, sequences=seqs, world=world, rank=rank, static_exchange=args.exchange == "static")
     if args.graph:
         dec.capture()
+        if os.environ.get("LEMOQ_VERBOSE"):
+            print("rank %d: step graph captured" % rank, file=sys.stderr, flush=True)
     # the literal configuration decodes 64 identical sequences; distinct first tokens make the exchange non-trivial
     first = torch.arange(dec.first_seq, dec.first_seq + dec.b, device=device, dtype=torch.int64)
     tokens = (first * 7 + 2) % model.config.vocab_size if not args.identical else torch.full_like(first, int(session.seed_token_id))
@@ -376,6 +379,9 @@ def run(args: Any) -> int:
     for _ in range(args.warmup):
         tokens = dec.step(tokens).float().argmax(dim=-1)
         history.append(tokens.clone())
+    if os.environ.get("LEMOQ_VERBOSE"):
+        torch.cuda.synchronize()
+        print("rank %d: warm-up steps done" % rank, file=sys.stderr, flush=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
@@ -414,6 +420,14 @@ def run(args: Any) -> int:
             torch.save(hist.cpu(), args.tokens_out)
     if world > 1:
         dist.barrier()
+        if args.graph:
+            # Tearing the communicator down while a captured graph still references its kernels blocked here
+            # (seen on B200 / NCCL 2.28): drop the graph, finish all work, and leave without the collective teardown.
+            dec.graph = None
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         dist.destroy_process_group()
     return 0
 
