@@ -317,7 +317,6 @@ def run_gpu(args) -> int:
         session.replay(synchronize=True)
     pinned_in = torch.zeros(4, dtype=torch.int64).pin_memory()
     pinned_out = torch.zeros(1, dtype=torch.int64).pin_memory()
-    dev_in = torch.zeros(4, dtype=torch.int64, device=device)
     b = session.buffers
     tok, pos = session.current_token_id, session.position
     barrier()
@@ -326,14 +325,14 @@ def run_gpu(args) -> int:
     with torch.cuda.stream(session.stream):
         e0.record(session.stream)
         for i in range(steps):
-            pinned_in[0], pinned_in[1], pinned_in[2] = tok, pos + i, pos + i + 1
-            dev_in.copy_(pinned_in, non_blocking=True)  # H2D of this step's inputs
-            b.token.copy_(dev_in[0:1].view(1, 1))
-            b.cache_position.copy_(dev_in[1:2])
-            b.position_ids.copy_(dev_in[1:2].view(1, 1))
-            b.filled_len.copy_(dev_in[2:3])
+            # H2D of this step's inputs: one 32-byte copy lands in all four step scalars (views of one buffer)
+            b.pack_step(pinned_in, token=tok, position=pos + i)
+            b.packed.copy_(pinned_in, non_blocking=True)
             session.graph.replay()
-            pinned_out.copy_(session.logits.reshape(-1).argmax().reshape(1), non_blocking=True)  # D2H of the result
+            picked = session.step_next_token  # the native step picks the token itself; the per-op engine leaves logits
+            if picked is None:
+                picked = session.logits.reshape(-1).argmax().reshape(1)
+            pinned_out.copy_(picked, non_blocking=True)  # D2H of the result
             session.stream.synchronize()
             tok = int(pinned_out[0])
         e1.record(session.stream)

@@ -300,6 +300,9 @@ typedef struct lemoq_step_desc {
     void* logits;           /* (vocab) fp16 output                                          */
     void* workspace;        /* lemoq_step_workspace_bytes() bytes, zeroed once by the caller */
     size_t workspace_bytes;
+    int64_t* next_token;    /* optional device scalar: the step also writes argmax(logits) here (the
+                               first maximal index, as the reference's greedy loop picks it:
+                               ref benchmarks/cudagraph.py:756-762); NULL = not wanted          */
 } lemoq_step_desc;
 
 typedef struct lemoq_step lemoq_step; /* host-side plan, owns no device memory */

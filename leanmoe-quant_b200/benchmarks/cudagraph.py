@@ -77,6 +77,7 @@ class GraphBuffers:
     attention_mask: Any
     next_token: Any
     filled_len: Any = None
+    packed: Any = None  # int64[4] holding token, cache_position, position_ids and (low half of slot 3) filled_len
 
     @classmethod
     def allocate(cls, device: Any, *, batch: int, max_cache_len: int | None = None, dtype: Any | None = None) -> "GraphBuffers":
@@ -86,14 +87,24 @@ class GraphBuffers:
             raise ValueError("GraphBuffers currently supports batch=1 only")
         max_cache_len = 1 if max_cache_len is None else max_cache_len
         dtype = torch.float32 if dtype is None else dtype
+        # The four step scalars are views of ONE 32-byte buffer, so that a caller with host-side inputs can
+        # update all of them with a single host->device copy (see pack_step()).
+        packed = torch.zeros(4, dtype=torch.long, device=device)
         return cls(
-            token=torch.zeros((batch, 1), dtype=torch.long, device=device),
-            cache_position=torch.zeros((1,), dtype=torch.long, device=device),
-            position_ids=torch.zeros((batch, 1), dtype=torch.long, device=device),
+            token=packed[0:1].view(batch, 1),
+            cache_position=packed[1:2],
+            position_ids=packed[2:3].view(batch, 1),
             attention_mask=torch.zeros((batch, 1, 1, max_cache_len), dtype=dtype, device=device),
             next_token=torch.zeros((batch, 1), dtype=torch.long, device=device),
-            filled_len=torch.zeros((1,), dtype=torch.int32, device=device),
+            filled_len=packed[3:4].view(torch.int32)[0:1],
+            packed=packed,
         )
+
+    @staticmethod
+    def pack_step(host: Any, *, token: int, position: int) -> Any:
+        """Fill a host int64[4] tensor with the image of the step scalars (little-endian int32 in slot 3)."""
+        host[0], host[1], host[2], host[3] = int(token), int(position), int(position), int(position) + 1
+        return host
 
     def set_step(self, *, token: int, position: int) -> None:
         self.token.fill_(int(token))
@@ -385,12 +396,14 @@ class StaticCacheDecodeSession:
         desc.filled_len = _cabi.ptr(self.buffers.filled_len)
         logits = torch.zeros((1, 1, cfg.vocab_size), dtype=self.dtype, device=self.device)
         desc.logits = _cabi.ptr(logits)
+        next_token = torch.zeros(1, dtype=torch.int64, device=self.device)  # the step's own greedy pick
+        desc.next_token = _cabi.ptr(next_token)
         nbytes = int(_cabi.lib().lemoq_step_workspace_bytes(ctypes.byref(desc)))
         workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         desc.workspace, desc.workspace_bytes = _cabi.ptr(workspace), nbytes
         handle = ctypes.c_void_p()
         _cabi.check(_cabi.lib().lemoq_step_create(ctypes.byref(desc), layers, ctypes.byref(handle)), "lemoq_step_create")
-        self._step = {"handle": handle, "logits": logits, "workspace": workspace, "keep": keep, "kv_int8": kv_int8,
+        self._step = {"handle": handle, "logits": logits, "next_token": next_token, "workspace": workspace, "keep": keep, "kv_int8": kv_int8,
                       "desc": desc, "layers": layers}
         self.capture_info["pdl"] = bool(self._use_pdl)
 
@@ -456,6 +469,13 @@ class StaticCacheDecodeSession:
         n = cfg.num_hidden_layers * cfg.num_experts_per_tok
         self.torch.cuda.synchronize()
         return self._step["workspace"][off: off + 8 * n].view(self.torch.int64).reshape(cfg.num_hidden_layers, -1).clone()
+
+    @property
+    def step_next_token(self) -> Any:
+        """Device scalar holding the token the native step engine picked in its last step (None for the per-op engine)."""
+        if self._step is None or self.capture_info.get("engine") != "step":
+            return None
+        return self._step["next_token"]
 
     def step_phase_times_us(self) -> Any:
         """Per-phase durations (us) of the last whole-step kernel: a (layers, 6) tensor for the phases
@@ -573,7 +593,9 @@ class StaticCacheDecodeSession:
                 self.graph.replay()
             if synchronize:
                 self.stream.synchronize()
-                self.current_token_id = int(self.logits.reshape(-1).argmax().item())
+                picked = self.step_next_token
+                # the native step engine picks the token itself (first maximal logit, like a host arg-max)
+                self.current_token_id = int(picked.item()) if picked is not None else int(self.logits.reshape(-1).argmax().item())
                 self.position += 1
             self.capture_info["replay_success"] = True
             return self.logits

@@ -144,6 +144,45 @@ __device__ __forceinline__ float norm_elem(__half x, float rstd, __half w) {
     return __half2float(__hmul(n, w));
 }
 
+// Block-wide arg-max over `n` fp16 values in global memory, the FIRST maximal index wins (the rule of a host
+// arg-max over the same row).  Every thread of the block calls it; thread 0 gets the result, others -1.
+// `red_v` / `red_i` hold >= 32 entries each.
+__device__ __forceinline__ int block_argmax_f16(const __half* __restrict__ v, int n, float* red_v, int* red_i) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    auto take = [&](float x, int i) {
+        if (x > best || (x == best && i < bi)) {
+            best = x;
+            bi = i;
+        }
+    };
+    const int chunks = (reinterpret_cast<uintptr_t>(v) & 15u) == 0 ? n / 8 : 0;
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        float f[8];
+        unpack8_h(ld_cg16(v + 8 * c), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) take(f[j], 8 * c + j);
+    }
+    for (int i = chunks * 8 + threadIdx.x; i < n; i += blockDim.x) take(__half2float(__ldcg(v + i)), i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        take(ob, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    if (lane == 0) {
+        red_v[warp] = best;
+        red_i[warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < nwarp; ++w) take(red_v[w], red_i[w]);
+        return bi;
+    }
+    return -1;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 

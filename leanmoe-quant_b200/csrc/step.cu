@@ -124,6 +124,14 @@ static int validate(const lemoq_step_desc& d) {
 }  // namespace lemoq
 
 namespace lemoq {
+// argmax(logits) -> *next_token, first maximal index (one block)
+__global__ void greedy_pick_kernel(const __half* logits, int n, int64_t* next_token) {
+    __shared__ float rv[32];
+    __shared__ int ri[32];
+    const int tok = block_argmax_f16(logits, n, rv, ri);
+    if (threadIdx.x == 0) *next_token = tok;
+}
+
 int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
 int g_mega_debug = 0;      // lemoq_set_tuning key 6: timing experiments of the whole-step kernel (wrong results)
 int g_mega_depth = 8;      // lemoq_set_tuning key 5: stages a warp of the whole-step kernel keeps in flight (capped by its ring)
@@ -254,6 +262,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.lm_codes = d.lm_head_codes;
         p.token = d.token; p.cache_position = d.cache_position; p.filled = d.filled_len;
         p.logits = reinterpret_cast<__half*>(d.logits);
+        p.next_token = d.next_token;
         p.L = s->mega_layers;
         p.err_flag = s->err_flag; p.bar_counter = s->bar_counter; p.bar_epoch = s->bar_epoch;
         p.attn_counters = s->attn_counters;
@@ -403,6 +412,13 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.err_flag = s->err_flag;
         if (!(g_step_skip_mask & 64))
             if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
+    }
+    if (d.next_token != nullptr) {
+        LaunchCfg plain = lc;
+        plain.pdl = false;
+        if (int rc = launch_kernel(greedy_pick_kernel, dim3(1), dim3(1024), 0, plain, reinterpret_cast<const __half*>(d.logits), d.vocab,
+                                   d.next_token))
+            return rc;
     }
     if (launches) *launches = count;
     return LEMOQ_OK;

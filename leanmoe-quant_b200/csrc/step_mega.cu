@@ -1125,6 +1125,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
             x_prev = p.xb;
         }
     }
+    if (p.next_token != nullptr && blockIdx.x == 0) {
+        // greedy pick on the device: all logits are visible after the last barrier
+        float* rv = reinterpret_cast<float*>(scratch);
+        int* ri = reinterpret_cast<int*>(scratch + 256);
+        const int tok = block_argmax_f16(p.logits, p.V, rv, ri);
+        if (threadIdx.x == 0) *p.next_token = tok;
+    }
     if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(p.bar_epoch, 1u);
 }
 

@@ -31,6 +31,7 @@ struct MegaParams {
     const int64_t *token, *cache_position;
     const int32_t* filled;
     __half* logits;
+    int64_t* next_token;  // optional: argmax(logits)
     const MegaLayer* L;  // device array
     int* err_flag;
     unsigned int *bar_counter, *bar_epoch, *attn_counters;
