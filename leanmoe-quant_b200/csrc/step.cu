@@ -182,7 +182,8 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
             if (ms < 1) ms = 1;
             if (ms > 9) ms = 9;  // the split merge of the whole-step kernel is unrolled for 9
             if (desc->attn_splits > 0 && desc->attn_splits < ms) ms = desc->attn_splits;
-            if (desc->heads * ms <= grid && ms <= splits) {
+            // (the partials buffer doubles as the per-block candidate list of the greedy pick: 2 floats per block)
+            if (desc->heads * ms <= grid && ms <= splits && desc->heads * splits * (desc->head_dim + 2) >= 2 * grid) {
                 MegaLayer* host = new (std::nothrow) MegaLayer[desc->layers + 1]();
                 if (host) {
                     for (int l = 0; l < desc->layers; ++l) {

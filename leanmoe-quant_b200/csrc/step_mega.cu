@@ -976,6 +976,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 
     const __half* x_prev = p.embed + (*p.token) * static_cast<int64_t>(p.H);
     float tw_reg = 0.f;
+    float pick_v = -INFINITY;  // greedy pick over the logits this warp produced
+    int pick_i = 0x7fffffff;
     int prep_par = 0;
     int l = 0, ph = 0;  // phase: 0 q.k.v / lm_head, 1 attention, 2 o_proj, 3 router, 4 gate/up, 5 down
     const int nphases = 6 * p.layers + 1;
@@ -1102,6 +1104,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                 const float a0 = t ? part[2] : part[0], a1 = t ? part[3] : part[1];
                 if (ph == 0) {
                     if (lane < 2) (last ? p.logits : p.qkv)[task * 2 + lane] = __float2half_rn(lane == 0 ? a0 : a1);
+                    if (last) {  // running greedy pick over this warp's logits (as stored: rounded to fp16), lowest index on ties
+                        const float v0 = __half2float(__float2half_rn(a0)), v1 = __half2float(__float2half_rn(a1));
+                        if (v0 > pick_v || (v0 == pick_v && task * 2 < pick_i)) {
+                            pick_v = v0;
+                            pick_i = task * 2;
+                        }
+                        if (v1 > pick_v || (v1 == pick_v && task * 2 + 1 < pick_i)) {
+                            pick_v = v1;
+                            pick_i = task * 2 + 1;
+                        }
+                    }
                 } else if (ph == 2) {
                     if (lane < 2) {
                         const int n = task * 2 + lane;
@@ -1117,6 +1130,28 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
             }
         }
         substamp(p, l, 2 * ph + 1);
+        if (last && p.next_token != nullptr) {
+            // this block's candidate for the greedy pick (the attention partials buffer is free by now)
+            float* cv = reinterpret_cast<float*>(scratch);
+            int* ci = reinterpret_cast<int*>(scratch + 256);
+            if (lane == 0) {
+                cv[warp] = pick_v;
+                ci[warp] = pick_i;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float best = cv[0];
+                int bi = ci[0];
+                for (int w = 1; w < kMegaWarps; ++w) {
+                    if (cv[w] > best || (cv[w] == best && ci[w] < bi)) {
+                        best = cv[w];
+                        bi = ci[w];
+                    }
+                }
+                p.attn_part[2 * blockIdx.x] = best;
+                p.attn_part[2 * blockIdx.x + 1] = __int_as_float(bi);
+            }
+        }
         bar.sync();
         stamp(p, step + 1);
         if (++ph == 6) {
@@ -1126,11 +1161,27 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
         }
     }
     if (p.next_token != nullptr && blockIdx.x == 0) {
-        // greedy pick on the device: all logits are visible after the last barrier
-        float* rv = reinterpret_cast<float*>(scratch);
-        int* ri = reinterpret_cast<int*>(scratch + 256);
-        const int tok = block_argmax_f16(p.logits, p.V, rv, ri);
-        if (threadIdx.x == 0) *p.next_token = tok;
+        // greedy pick on the device: one candidate per block (written before the last barrier), merged here
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int b = lane; b < static_cast<int>(gridDim.x); b += 32) {
+            const float v = __ldcg(p.attn_part + 2 * b);
+            const int i = __float_as_int(__ldcg(p.attn_part + 2 * b + 1));
+            if (v > best || (v == best && i < bi)) {
+                best = v;
+                bi = i;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) {
+                best = ob;
+                bi = oi;
+            }
+        }
+        if (threadIdx.x == 0) *p.next_token = bi;
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(p.bar_epoch, 1u);
 }
