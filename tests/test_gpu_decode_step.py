@@ -289,3 +289,40 @@ def _full_model_greedy(ctx, expect_kernels):
     # routings identical and most steps identical in every layer; KL and tokens above bound the effect.
     assert pair_match >= 0.98 * pairs, (pair_match, pairs)
     assert id_match >= steps // 2, id_match
+
+
+@pytest.mark.parametrize("whole", [True, False])
+def test_out_of_range_step_scalars_raise_flags_instead_of_faulting(whole):
+    """A position / length beyond the cache capacity is clamped by the kernels and reported through the flag
+    word (LEMOQ_FLAG_BAD_POSITION = 1, LEMOQ_FLAG_BAD_LENGTH = 2); nothing is written outside the caches."""
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+    from lemoq import _cabi
+
+    _cabi.call("lemoq_set_tuning", 4, 1 if whole else 0)
+    try:
+        spec = glue.OlmoeSpec(layers=1, vocab=2048)
+        ctx, new = 64, 2
+        wf = glue.random_float_weights(spec, seed=2, dtype=torch.float16, std=0.02)
+        model = lemoq_model_from_oracle(wf)
+        install_canonical(model, ctx, new)
+        prompt = torch.full((1, ctx), 1, dtype=torch.long, device=DEV)
+        session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=new, engine="step")
+        session.capture(warmup=1)
+        assert session.capture_info["kernels_per_step"] == (1 if whole else session.capture_info["kernels_per_step"])
+        session.reset()
+        session.replay(synchronize=True)
+        assert session.step_error_flags() == 0
+        before = [cl.keys.clone() for cl in session.cache.layers]
+        cap = session.config.max_cache_len
+        session.buffers.cache_position.fill_(cap + 5)
+        session.buffers.filled_len.fill_(cap + 7)
+        with torch.cuda.stream(session.stream):
+            session.graph.replay()
+        session.stream.synchronize()
+        assert session.step_error_flags() == 1 | 2
+        assert torch.isfinite(session.logits.float()).all()
+        for cl, b in zip(session.cache.layers, before):
+            assert torch.equal(cl.keys, b)  # the out-of-range row was not written anywhere
+        session.close()
+    finally:
+        _cabi.call("lemoq_set_tuning", 4, 1)
