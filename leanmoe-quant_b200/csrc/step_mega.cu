@@ -689,6 +689,14 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
             const float t = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
             s = fmaf(t, qsx[c], s);
         }
+        // the value codes of the block (the key registers are free now): in flight during the softmax reductions
+        uint32_t vw[32];
+        {
+            const int lastj = min(32, ac.n_end - base) - 1;
+            const int8_t* vrow = vc + static_cast<int64_t>(base) * D + lane * 4;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) vw[j] = __ldcg(reinterpret_cast<const uint32_t*>(vrow + static_cast<int64_t>(min(j, lastj)) * D));
+        }
         s = has ? s * kscale : -INFINITY;
         const float m_new = fmaxf(m_i, warp_max(s));  // finite: lane 0 always has a position
         const float alpha = exp2f(m_i - m_new);
@@ -701,20 +709,13 @@ __device__ __noinline__ void attention_phase(const MegaParams& p, const MegaLaye
         sm.pbuf[warp][lane] = pw * vscale;
         __syncwarp();
         const int cnt = min(32, ac.n_end - base);
-        const int8_t* vrow = vc + static_cast<int64_t>(base) * D + lane * 4;
-#pragma unroll 1
-        for (int j0 = 0; j0 < cnt; j0 += 16) {
-            uint32_t vw[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) vw[j] = __ldcg(reinterpret_cast<const uint32_t*>(vrow + static_cast<int64_t>(min(j0 + j, cnt - 1)) * D));
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float pj = j0 + j < cnt ? sm.pbuf[warp][j0 + j] : 0.f;
-                acc[0] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] & 0xffu)), acc[0]);
-                acc[1] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 8) & 0xffu)), acc[1]);
-                acc[2] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 16) & 0xffu)), acc[2]);
-                acc[3] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] >> 24)), acc[3]);
-            }
+        for (int j = 0; j < 32; ++j) {
+            const float pj = j < cnt ? sm.pbuf[warp][j] : 0.f;
+            acc[0] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] & 0xffu)), acc[0]);
+            acc[1] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 8) & 0xffu)), acc[1]);
+            acc[2] = fmaf(pj, static_cast<float>(static_cast<int8_t>((vw[j] >> 16) & 0xffu)), acc[2]);
+            acc[3] = fmaf(pj, static_cast<float>(static_cast<int8_t>(vw[j] >> 24)), acc[3]);
         }
     }
     // ---- merge the warps of the block ----------------------------------------------------------------------
