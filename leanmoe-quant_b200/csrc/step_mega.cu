@@ -1045,9 +1045,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
 #pragma unroll 1
         for (int i = 0; i < ntasks; i += rows2 ? 2 : 1) {
             const bool two = rows2 ? i + 1 < ntasks : nst > 1;
+            const bool prof = ph == 5 && i == 0;
+            if (prof) dbg_clock(p, 50);
             const unsigned char* st0 = ws.acquire();
             const unsigned char* st1 = two ? ws.acquire_next() : st0;
             if (!st0 || !st1) break;
+            if (prof) dbg_clock(p, 51);
             float part[4] = {0.f, 0.f, 0.f, 0.f};
             if (rows2) {
                 const __half* sc0 = reinterpret_cast<const __half*>(st0 + 2 * K);
@@ -1096,9 +1099,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                     }
                 }
             }
+            if (prof) dbg_clock(p, 52);
             ws.release(two ? 2 : 1);
+            if (prof) dbg_clock(p, 53);
 #pragma unroll
             for (int r = 0; r < 4; ++r) part[r] = warp_sum(part[r]);
+            if (prof) dbg_clock(p, 54);
 #pragma unroll 1
             for (int t = 0; t < (rows2 && two ? 2 : 1); ++t) {
                 const int task = ws.wg + (i + t) * ws.G;
@@ -1130,6 +1136,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) step_mega_kernel(const __grid
                 }
             }
         }
+        if (ph == 5) dbg_clock(p, 55);
         substamp(p, l, 2 * ph + 1);
         if (last && p.next_token != nullptr) {
             // this block's candidate for the greedy pick (the attention partials buffer is free by now)
