@@ -115,6 +115,29 @@ def bench_moe(timer: Timer, tokens_list, peak: float) -> None:
         us = timer.cold(both, setup)
         report("moe_grouped_w8 (gate_up+down)", distinct * per_expert_w8 + t * h * 2 * 2, us, timer.floor_us, peak, tokens=t,
                distinct_experts=distinct, note="bytes count each distinct expert once")
+        if t > 1:
+            # the many-token form: pairs sorted by expert, weights-stationary kernels (each distinct expert read once)
+            from lemoq.kernels.batched_w8 import w8_experts_tokens
+
+            def sorted_pairs():
+                flat = state["ids"].reshape(-1)
+                order = torch.argsort(flat, stable=True)
+                state["pair_x"] = x[torch.div(order, k, rounding_mode="floor")].contiguous()
+                state["pair_e"] = flat[order].contiguous()
+
+            def setup_pairs(i):
+                setup(i)
+                sorted_pairs()
+
+            def many():
+                w8_experts_tokens(state["pair_x"], state["pair_e"], gu_c, gu_s, dn_c, dn_s, group_size=128)
+
+            setup_pairs(0)
+            distinct = int(torch.unique(state["ids"]).numel())
+            us = timer.cold(many, setup_pairs)
+            report("moe_w8 many-token kernels (quantise + gate_up + quantise + down, pairs sorted by expert)",
+                   distinct * per_expert_w8 + t * h * 2 * 2, us, timer.floor_us, peak, tokens=t, distinct_experts=distinct,
+                   note="bytes count each distinct expert once; the sort and the routing-weighted combine are outside")
         if t == 1:
             us = timer.cold(gate_up, setup)
             report("moe_gate_up_w8", k * (2 * f * h + 2 * f * (h // 128) * 2) + h * 2 + k * f * 2, us, timer.floor_us, peak, tokens=t)
@@ -145,6 +168,24 @@ def bench_moe(timer: Timer, tokens_list, peak: float) -> None:
     us = timer.cold(both16, setup16)
     report("moe_grouped_fp16 (gate_up+down)", k * 3 * f * h * 2 + h * 4, us, timer.floor_us, peak, tokens=1)
     _ = grouped_moe_forward
+
+
+def bench_dense_tokens(timer: Timer, peak: float) -> None:
+    """The weights-stationary dense kernel at the q.k.v and lm_head shapes for 16 and 64 tokens."""
+    from lemoq.kernels.batched_w8 import quantise_tokens, w8_rows_tokens
+
+    for name, n in (("qkv 6144x2048", 6144), ("lm_head 50304x2048", 50304)):
+        g = torch.Generator(device=DEV).manual_seed(n)
+        codes = torch.randint(-127, 128, (n, 2048), generator=g, dtype=torch.int8, device=DEV)
+        scale = (torch.randn(n, 16, generator=g, device=DEV).abs() * 0.01).half()
+        for t in (16, 64):
+            x = torch.randn(t, 2048, generator=g, device=DEV).half()
+
+            def run():
+                w8_rows_tokens(quantise_tokens(x), t, codes, scale, group_size=128)
+
+            us = timer.cold(run, lambda i: None)
+            report("dense_w8 many-token kernel %s" % name, n * 2048 + n * 16 * 2 + t * 2048 * 2 + t * n * 2, us, timer.floor_us, peak, tokens=t)
 
 
 def bench_dense(timer: Timer, peak: float) -> None:
@@ -217,6 +258,7 @@ def main() -> int:
         bench_moe(timer, [int(t) for t in args.tokens.split(",")], peak)
     if args.subject in ("dense", "all"):
         bench_dense(timer, peak)
+        bench_dense_tokens(timer, peak)
     if args.subject in ("attn", "all"):
         bench_attn(timer, peak)
     return 0
