@@ -207,6 +207,11 @@ def _one_full_size_layer(expect_kernels, ctx=1024):
         session.replay(synchronize=True)
         results[engine] = session.logits_cpu().reshape(-1)
         if engine == "step":
+            # no data atomics anywhere: the same step from the same state gives the same bits
+            session.reset()
+            session.current_token_id = 7
+            session.replay(synchronize=True)
+            assert torch.equal(session.logits_cpu().reshape(-1), results[engine])
             ids = session.step_topk_ids()[0].cpu().tolist()
             assert session.step_error_flags() == 0
             if expect_kernels is not None:
