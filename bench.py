@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--ctx 1024] [--impl reference]
 
-Workload (BASELINE config 2): full OLMoE-1B-7B architecture (16 layers, hidden 2048, 64 experts top-8,
+Workload (benchmark configuration 2): full OLMoE-1B-7B architecture (16 layers, hidden 2048, 64 experts top-8,
 expert FFN 1024, vocab 50304), seeded random-init fp16 weights, canonical quantisation W8A16 g128 +
 lm_head W8 + per-token INT8 KV, all-ones prompt of ``ctx`` tokens prefilled, then greedy decode.
 A "step" is one decoded token = one replay of the captured step graph.
@@ -359,7 +359,7 @@ def run_gpu(args) -> int:
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, "
-                               "ctx %d, one CUDA graph per step (BASELINE config 2)" % ctx,
+                               "ctx %d, one CUDA graph per step (benchmark configuration 2)" % ctx,
                    "ctx": ctx, "layers": model.config.num_hidden_layers, "engine": session.capture_info.get("engine"),
                    "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0",
                    "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (budget["T"] / 1e9),

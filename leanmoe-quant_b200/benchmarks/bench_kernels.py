@@ -8,7 +8,7 @@ Every timed call is one launch (or the two launches of the grouped MoE layer) be
 the current stream, preceded by a 256 MB memset that evicts L2; the median is reported together with
 the empty event-pair floor, and GB/s = analytic bytes / (time - floor) as well as / time.
 
-Subjects (BASELINE config 4 and the per-kernel evidence rows):
+Subjects (benchmark configuration 4 and the per-kernel evidence rows):
   moe    grouped expert GEMV, 64 experts top-8, gate/up [64, 2x1024, 2048], down [64, 2048, 1024]:
          int8 g128 weights with fp16 scales |N(0,1)|*0.01 and the fp16-weight variant, 1/4/16 tokens
   dense  W8 dequant GEMV at the q.k.v (6144x2048), o_proj (2048x2048) and lm_head (50304x2048) shapes

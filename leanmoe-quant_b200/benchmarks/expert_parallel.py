@@ -1,4 +1,4 @@
-"""Batched expert-parallel decode (BASELINE config 5): B sequences in lockstep, the attention/dense part
+"""Batched expert-parallel decode (benchmark configuration 5): B sequences in lockstep, the attention/dense part
 data-parallel over the sequences (weights replicated, every rank owns B/G sequences and their int8 KV),
 the MoE expert-parallel (expert e lives on rank e // (E/G)).
 
@@ -408,7 +408,7 @@ def run(args: Any) -> int:
                   "n_gpus": world, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                   "scaling": "strong", "data": "synthetic",
                   "config": {"workload": "%d sequences x ctx %d lockstep greedy decode, W8A16 + INT8 KV, experts sharded %d per GPU, "
-                                         "NCCL all-to-all dispatch/combine (BASELINE config 5)" % (seqs, ctx, model.config.num_experts // world),
+                                         "NCCL all-to-all dispatch/combine (benchmark configuration 5)" % (seqs, ctx, model.config.num_experts // world),
                              "layers": model.config.num_hidden_layers, "identical_sequences": bool(args.identical),
                              "exchange": args.exchange, "cuda_graph": bool(args.graph)},
                   "error_flags": flags}

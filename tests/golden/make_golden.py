@@ -304,7 +304,7 @@ def gen_layer_trace(out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (its src/ is put on sys.path)")
     args = ap.parse_args()
     sys.path[:0] = [os.path.join(args.reference, "src"), args.reference]
     torch.set_num_threads(1)  # fixed reduction order inside the generators

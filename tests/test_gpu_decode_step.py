@@ -1,7 +1,7 @@
 """End-to-end decode parity on the GPU: the captured step (native step engine and per-op engine)
 against the CPU oracle on identical seeded weights and an identical prefilled cache.
 
-Gates (BASELINE north_star): weight codes and top-k expert ids bit-exact, logits KL < 1e-3 and
+Gates (the stated parity gates): weight codes and top-k expert ids bit-exact, logits KL < 1e-3 and
 greedy tokens identical over the decode steps.
 """
 
@@ -175,7 +175,7 @@ def test_one_full_size_layer_chained_kernels(chained_kernels):
 
 
 def test_one_full_size_layer_whole_step_kernel_ctx_4096(whole_step_kernel):
-    """BASELINE config 3's length: every warp of an attention block walks more than one block of positions."""
+    """benchmark configuration 3's length: every warp of an attention block walks more than one block of positions."""
     _one_full_size_layer(expect_kernels=1, ctx=4096)
 
 

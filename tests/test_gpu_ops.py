@@ -1,6 +1,6 @@
 """GPU parity of every kernel against the CPU oracle, through the C-ABI (via the lemoq op API).
 
-Gates (BASELINE north_star): int8 weight/KV codes, scales and top-k expert ids bit-exact;
+Gates (the stated parity gates): int8 weight/KV codes, scales and top-k expert ids bit-exact;
 per-kernel fp16 outputs within 2e-3 relative error (max |err| / max |ref|).
 """
 
