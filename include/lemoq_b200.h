@@ -183,9 +183,12 @@ LEMOQ_API int lemoq_attn_decode_int8(const void* q, const int8_t* kc, const void
  * lemoq_attn_decode_int8 on the same inputs.
  * The split partials and arrival counters live in a fixed array inside the library
  * (lemoq_attn_static_scratch_bytes() = 1 MiB per device).  The call allocates and
- * frees nothing, and neither does anything it calls.  Sizes whose scratch need
- * (256-byte-rounded 4*heads + 4*heads*num_splits*(D+2) bytes) exceeds the array
- * are refused with LEMOQ_ERR_INVALID and a message in lemoq_last_error().
+ * frees nothing, and neither does anything it calls.  The first 16 KiB of the array
+ * are the arrival counters (at most 4096 heads), the partials follow: sizes with
+ * 16384 + 4*heads*num_splits*(D+2) bytes above the array's size are refused with
+ * LEMOQ_ERR_INVALID and a message in lemoq_last_error().  Each call clears its
+ * counters on the stream ahead of its kernel; the partials keep the last call's
+ * contents and are written before they are read.
  * The first call on a device looks the array's address up (once per device, with
  * that device current); make that first call outside any stream capture.
  * All calls on a device share the array: calls whose kernels may overlap on the

@@ -323,15 +323,21 @@ int launch_attn_decode(const AttnParams& p, bool int8_kv, bool fused, const Laun
 // counters of the attention kernel live in the fixed array below, which is part of the library image:
 // nothing is allocated or freed, here or in any routine this entry point calls.
 //
-// The array holds kStaticAttnScratchBytes (1 MiB); a call whose heads x splits x (D + 2) partials plus
-// counters need more is refused with LEMOQ_ERR_INVALID.  The array starts zeroed when the module is
-// loaded (the counters must start at zero; every launch leaves them at zero again).  ALL calls on a
-// device share the one array: two calls whose kernels may run at the same time on that device (other
-// streams, other threads) race on it and give wrong results - order them on one stream.
+// The array holds kStaticAttnScratchBytes (1 MiB).  Its first kStaticAttnCounterBytes (16 KiB) are the
+// arrival counters of up to 4096 heads, at the same place for every shape; the split partials of the
+// call start right behind them.  A call with more heads, or whose heads x splits x (D + 2) partials do
+// not fit behind the counters, is refused with LEMOQ_ERR_INVALID.  The counters must be zero when a
+// launch starts: the array is zeroed when the module is loaded, every launch leaves its counters at
+// zero again, and each call also enqueues a clear of its own counters ahead of its kernel, so a launch
+// that was aborted earlier cannot poison later calls.  The partials keep the last call's contents; they
+// are always written before they are read.  ALL calls on a device share the one array: two calls whose
+// kernels may run at the same time on that device (other streams, other threads) race on it and give
+// wrong results - order them on one stream.
 // ---------------------------------------------------------------------------------------------------
 namespace {
 
 constexpr size_t kStaticAttnScratchBytes = size_t(1) << 20;
+constexpr size_t kStaticAttnCounterBytes = size_t(16) << 10;  // fixed counter region: 4096 heads
 constexpr int kStaticMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
@@ -374,8 +380,12 @@ extern "C" int lemoq_attn_decode_int8_static(const void* q, const int8_t* kc, co
                   "attn_decode_int8_static: codes must be 16-byte aligned with a head stride that is a multiple of 16");
     LEMOQ_REQUIRE(kv_head_stride >= static_cast<int64_t>(S) * D, LEMOQ_ERR_INVALID,
                   "attn_decode_int8_static: heads overlap (head stride < S*D)");
-    // same layout as the workspace of lemoq_attn_decode_int8: counters in a 256-byte slot, then the partials
-    const size_t counters = (sizeof(unsigned int) * static_cast<size_t>(heads) + 255) / 256 * 256;
+    // counters in a region of fixed size (so that calls of different shapes never lay partials over
+    // another shape's counters), then the partials
+    LEMOQ_REQUIRE(sizeof(unsigned int) * static_cast<size_t>(heads) <= kStaticAttnCounterBytes, LEMOQ_ERR_INVALID,
+                  "attn_decode_int8_static: heads=%d, the fixed array holds counters for %zu heads", heads,
+                  kStaticAttnCounterBytes / sizeof(unsigned int));
+    const size_t counters = kStaticAttnCounterBytes;
     const size_t need = counters + sizeof(float) * static_cast<size_t>(heads) * num_splits * (D + 2);
     LEMOQ_REQUIRE(need <= kStaticAttnScratchBytes, LEMOQ_ERR_INVALID,
                   "attn_decode_int8_static: heads=%d x num_splits=%d x head_dim=%d needs %zu bytes of scratch, the fixed array holds %zu",
@@ -401,6 +411,9 @@ extern "C" int lemoq_attn_decode_int8_static(const void* q, const int8_t* kc, co
     p.kv_head_stride = kv_head_stride;
     LaunchCfg lc;
     lc.stream = static_cast<cudaStream_t>(stream);
+    // the counters of this call start at zero whatever an earlier (possibly aborted) launch left behind
+    const cudaError_t cerr = cudaMemsetAsync(scratch, 0, sizeof(unsigned int) * static_cast<size_t>(heads), lc.stream);
+    if (cerr != cudaSuccess) return set_error(LEMOQ_ERR_CUDA, "attn_decode_int8_static: clearing the counters: %s", cudaGetErrorString(cerr));
     return launch_attn_decode(p, true, false, lc);
 }
 
