@@ -368,7 +368,8 @@ def run_gpu(args) -> int:
         "floor_fraction": floor_ms / dev_ms, "floor_fraction_e2e": floor_ms / e2e_ms,
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": 32,
                 "d2h_bytes_per_step": 8},
-        "gpu_launches": launches_per_step * steps * 2, "kernels_per_step": launches_per_step, "clocks": clocks,
+        "gpu_launches": launches_per_step * steps * 2, "kernels_per_step": launches_per_step,
+        "step_kernel": session.capture_info.get("step_kernel"), "clocks": clocks,
     }
     if rank == 0:
         isolated = time_dominant_kernel(model, peaks)
@@ -377,7 +378,8 @@ def run_gpu(args) -> int:
             # duration is the device-timed step of the timed region above (CUDA events on the launching stream).
             achieved = budget["T"] / (dev_ms * 1e-3) / 1e9
             result["roofline"] = {
-                "bound": "hbm", "kernel": "step_mega_kernel (whole decode step: 16 x 6 phases + lm_head)",
+                "bound": "hbm", "kernel": "%s (whole decode step: 16 x 6 phases + lm_head)"
+                                          % {"tile": "step_tile_kernel", "rows": "step_mega_kernel"}.get(session.capture_info.get("step_kernel"), "?"),
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "traffic": WHOLE_STEP_DRAM_TRAFFIC.get((ctx, model.config.num_hidden_layers)),
                 "bytes_per_launch": budget["T"], "us_per_launch": dev_ms * 1e3, "peak_source": peaks["source"],

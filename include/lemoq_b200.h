@@ -323,6 +323,10 @@ LEMOQ_API int* lemoq_step_error_flag(lemoq_step* step);
  * checks): top_i (layers, top_k) int64 and router logits (layers, experts) fp16. */
 LEMOQ_API const int64_t* lemoq_step_topk_ids(lemoq_step* step);
 LEMOQ_API const void* lemoq_step_router_logits(lemoq_step* step);
+/* Name of the kernel form the plan runs as: "tile" (one cooperative kernel per step on 8-row tiles and the int8
+ * tensor-core dot product), "rows" (one cooperative kernel per step on row pairs and the integer dot-product
+ * instruction) or "chained" (6 kernels per layer).  Static string.  No counterpart in the reference. */
+LEMOQ_API const char* lemoq_step_engine(lemoq_step* step);
 /* Device pointer to 6*layers + 2 global-timer stamps (ns) taken by the whole-step kernel at its start and
  * after each phase barrier of the last step; NULL when the step runs as chained kernels. */
 LEMOQ_API const unsigned long long* lemoq_step_phase_stamps(lemoq_step* step);
@@ -331,6 +335,7 @@ LEMOQ_API const unsigned long long* lemoq_step_phase_stamps(lemoq_step* step);
 #define LEMOQ_FLAG_BAD_LENGTH 2
 #define LEMOQ_FLAG_BAD_EXPERT 4
 #define LEMOQ_FLAG_WAIT_TIMEOUT 8 /* a bounded wait on an async copy gave up */
+#define LEMOQ_FLAG_BAD_TOKEN 16   /* *token outside [0, vocab): clamped */
 
 #ifdef __cplusplus
 }

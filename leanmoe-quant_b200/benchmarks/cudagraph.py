@@ -441,6 +441,7 @@ class StaticCacheDecodeSession:
             _cabi.check(_cabi.lib().lemoq_step_run(self._step["handle"], _cabi.current_stream(self.device), ctypes.byref(n)),
                         "lemoq_step_run")
             self.capture_info["kernels_per_step"] = int(n.value)
+            self.capture_info["step_kernel"] = _cabi.lib().lemoq_step_engine(self._step["handle"]).decode()
             return self._step["logits"]
         output = self.model(self.buffers.token, attention_mask=self.buffers.attention_mask, past_key_values=self.cache,
                             use_cache=True, cache_position=self.buffers.cache_position, position_ids=self.buffers.position_ids)

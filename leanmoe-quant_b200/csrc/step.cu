@@ -42,6 +42,8 @@ struct lemoq_step {
     unsigned int* bar_epoch;
     lemoq::MegaLayer* mega_layers;  // device copy of the layer descriptors
     int mega_grid;                  // 0 = chained kernels
+    int tile_kernel;                // the whole-step kernel is the tile form (step_tile.cu)
+    float* stats;                   // per-block sums of squares of the q / k rows (tile form)
     unsigned long long* stamps;     // phase time stamps of the whole-step kernel
 };
 
@@ -93,10 +95,11 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(top_w, __half*, sizeof(__half) * d.top_k);
     LEMOQ_TAKE(top_i, int64_t*, sizeof(int64_t) * d.layers * d.top_k);
     LEMOQ_TAKE(attn_part, float*, sizeof(float) * d.heads * splits * (d.head_dim + 2));
+    LEMOQ_TAKE(stats, float*, sizeof(float) * 2 * 1024);
     LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * (d.layers + 1));
-    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 128));
+    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 256));
 #undef LEMOQ_TAKE
     return c.off;
 }
@@ -173,14 +176,20 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
     s->splits = splits;
     carve(*desc, splits, s);
     s->mega_grid = 0;
-    if (g_step_use_mega && getenv("LEMOQ_VERBOSE")) fprintf(stderr, "lemoq: whole-step kernel eligible: %d\n", (int)mega_eligible(*desc));
-    if (g_step_use_mega && mega_eligible(*desc)) {
-        const int grid = mega_grid(*desc, splits);
+    s->tile_kernel = 0;
+    const bool want_tile = g_step_use_mega == 1 && tile_eligible(*desc);
+    const bool want_mega = g_step_use_mega != 0 && mega_eligible(*desc);
+    if (getenv("LEMOQ_VERBOSE")) fprintf(stderr, "lemoq: whole-step kernel eligible: tile %d, row form %d\n", (int)want_tile, (int)want_mega);
+    if (want_tile || want_mega) {
+        int grid = want_tile ? tile_grid(*desc) : 0;
+        const bool use_tile = grid > 0 && grid <= 1024;
+        if (!use_tile) grid = want_mega ? mega_grid(*desc, splits) : 0;
         if (grid > 0) {
             // attention units are (head, split) blocks: at most one per resident block
             int ms = grid / desc->heads;
             if (ms < 1) ms = 1;
             if (ms > 9) ms = 9;  // the split merge of the whole-step kernel is unrolled for 9
+            if (use_tile) ms = tile_attention_splits(*desc, grid);
             if (desc->attn_splits > 0 && desc->attn_splits < ms) ms = desc->attn_splits;
             // (the partials buffer doubles as the per-block candidate list of the greedy pick: 2 floats per block)
             if (desc->heads * ms <= grid && ms <= splits && desc->heads * splits * (desc->head_dim + 2) >= 2 * grid) {
@@ -218,6 +227,7 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
                     delete[] host;
                     if (err == cudaSuccess) {
                         s->mega_grid = grid;
+                        s->tile_kernel = use_tile ? 1 : 0;
                         s->splits = ms;
                     }
                 }
@@ -237,6 +247,10 @@ extern "C" void lemoq_step_destroy(lemoq_step* s) {
 extern "C" int* lemoq_step_error_flag(lemoq_step* s) { return s ? s->err_flag : nullptr; }
 extern "C" const int64_t* lemoq_step_topk_ids(lemoq_step* s) { return s ? s->top_i : nullptr; }
 extern "C" const void* lemoq_step_router_logits(lemoq_step* s) { return s ? s->router_logits : nullptr; }
+extern "C" const char* lemoq_step_engine(lemoq_step* s) {
+    if (!s || s->mega_grid <= 0 || !g_step_use_mega) return "chained";
+    return s->tile_kernel ? "tile" : "rows";
+}
 extern "C" const unsigned long long* lemoq_step_phase_stamps(lemoq_step* s) { return (s && s->mega_grid > 0) ? s->stamps : nullptr; }
 
 extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
@@ -269,11 +283,14 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.attn_counters = s->attn_counters;
         p.qkv = s->qkv; p.attn = s->attn; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
         p.router_logits = s->router_logits; p.top_w = s->top_w; p.top_i = s->top_i; p.attn_part = s->attn_part;
+        p.stats = s->stats;
         p.barriers_per_launch = 6 * d.layers + 1;
         p.stamps = s->stamps;
         p.depth = g_mega_depth;
         p.debug = g_mega_debug;
-        if (int rc = launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream))) return rc;
+        if (int rc = s->tile_kernel ? launch_step_tile(p, s->mega_grid, static_cast<cudaStream_t>(stream))
+                                    : launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream)))
+            return rc;
         if (launches) *launches = 1;
         return LEMOQ_OK;
     }

@@ -38,6 +38,7 @@ struct MegaParams {
     __half *qkv, *attn, *xa, *xb, *act, *router_logits, *top_w;
     int64_t* top_i;
     float* attn_part;
+    float* stats;                // tile kernel: per-block sums of squares of the q rows, then of the k rows (2 x grid floats)
     int barriers_per_launch;
     int debug;                   // timing experiments (wrong results)
     int depth;                   // stages a warp keeps in flight (clamped to the ring size)
@@ -48,5 +49,12 @@ size_t mega_smem_bytes();
 bool mega_eligible(const lemoq_step_desc& d);
 int mega_grid(const lemoq_step_desc& d, int splits);  // blocks to launch (one per SM), 0 = unavailable
 int launch_step_mega(const MegaParams& p, int grid, cudaStream_t stream);
+
+// the same step on 16-row tiles and the int8 tensor-core dot product (step_tile.cu)
+size_t tile_smem_bytes();
+bool tile_eligible(const lemoq_step_desc& d);
+int tile_grid(const lemoq_step_desc& d);  // blocks to launch (one per SM), 0 = unavailable
+int tile_attention_splits(const lemoq_step_desc& d, int grid);
+int launch_step_tile(const MegaParams& p, int grid, cudaStream_t stream);
 
 }  // namespace lemoq

@@ -1,0 +1,1343 @@
+// The whole decode step as ONE persistent cooperative kernel, built on 8-row weight tiles and the
+// int8 tensor-core dot product.
+//
+// One block per SM stays resident for the whole step; the phases of a layer are separated by a grid
+// barrier.  All weights move as TILES: 8 whole rows (+ the rows' group scales) brought into a
+// shared-memory stage by bulk asynchronous copies, one copy per row (rows land 64 bytes apart from
+// the natural stride, which keeps the 128-bit shared loads below free of bank conflicts).  Ten warps
+// of the block own one stage each and fill it IN THEIR OWN PROGRAM ORDER ACROSS PHASES, so while a
+// warp waits at a barrier the tiles of its next phases (q.k.v, KV cache, o_proj, router and lm_head
+// tiles do not depend on activations) are already landing; only the expert tiles have to wait for
+// the routing.
+//
+// Arithmetic: the activation vector of a phase is turned once per block into three planes of signed
+// 7-bit digits with one power-of-two scale per group of 128 (x = sx * (d2*2^14 + d1*2^7 + d0)).  The
+// planes are the B operand of mma.sync m16n8k32 s8, the int8 weight codes are the A operand as they
+// sit in memory.  The 16 rows of the instruction are the 8 rows of the tile, twice: rows 0-7 take the
+// first half of k, rows 8-15 the second half, and B carries the planes of the first half in columns
+// 0-2 and those of the second half in columns 3-5.  One instruction thus multiplies 8 rows x 64 codes;
+// the int32 sums of a 128-group are exact and are scaled by (row scale x sx) in fp32.  The bytes a
+// lane loads for A and B are a permutation of k inside a 64-byte chunk, the same on both sides, so
+// 128-bit shared loads feed the fragments directly.  The router rows (fp16) go through mma.sync
+// m16n8k16 f16 the same way: 4 rows x 4 quarters of k, the fp16 activations of the quarters in
+// columns 0-3.
+//
+// A warp finishes the rows of its tile by itself (fp16 rounding, residual add, SwiGLU of a tile of
+// 4 gate + 4 up rows); only the expert down rows, whose eight routed experts are eight tiles, leave
+// partial sums in shared memory that the block adds in slot order.  No atomics on data: results are
+// bit-identical run to run.
+//
+// Phases per layer:
+//   A  q.k.v tiles          x = RMSNorm(x_prev) planes                          -> qkv, sum-of-squares partials
+//   B  attention            one (head, split) per block; KV tiles of 64 positions stream through the same
+//                           stages; fused q/k norm + RoPE + KV write            -> (m, l, acc) partial per unit
+//   C  o_proj tiles         the splits of each head are merged while the planes are built; + residual -> x1
+//   D  router tiles (fp16)  h2 = RMSNorm(x1) planes stay in shared memory for E   -> router logits
+//   E  expert gate/up       one warp per block derives the top-k; SwiGLU          -> act
+//   F  expert down          routing-weighted sum + residual                       -> x2
+// then the lm_head tiles on RMSNorm(x2) as the q.k.v tiles of a pseudo layer, with the greedy pick.
+#include <algorithm>
+#include <cstddef>
+#include <cstdio>
+#include <cstdlib>
+
+#include "step_mega.h"
+#include "stream.cuh"
+
+namespace lemoq {
+namespace tile {
+
+constexpr int kStreamWarps = 10;        // consumer warps: one stage each, they do all the arithmetic
+constexpr int kProducerWarps = 5;       // producer warps: each keeps two stages filled, nothing else
+constexpr int kWarps = kStreamWarps;    // warps that take part in the block-wide work of a phase
+constexpr int kConsumerThreads = kStreamWarps * 32;
+constexpr int kThreads = (kStreamWarps + kProducerWarps) * 32;
+constexpr int kPad = 64;                // plane segments and vector quarters sit 64 bytes off their natural stride
+constexpr int kScaleOff = 8 * 2048;     // the group scales of a tile sit behind its rows
+constexpr int kStageBytes = kScaleOff + 256;
+constexpr int kKvTile = 64;             // cached positions per attention tile
+constexpr int kMaxLayers = 33;
+constexpr int kMaxSplits = 9;
+constexpr int kHeadDim = 128;
+constexpr int kQPlaneStride = kHeadDim + kPad;
+constexpr int kPartFloats = 1024;       // partial sums of the down phase (8 per tile)
+constexpr uint32_t kBarrierSpinLimit = 1u << 24;
+
+enum Kind : int { KA = 0, KB = 1, KC = 2, KD = 3, KE = 4, KF = 5, KEND = 6 };
+
+// ---------------------------------------------------------------------------------------------
+// small device helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add(unsigned int* p, unsigned int v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint2 ld_cg8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+// Block barrier of the consumer warps (the producer warps never take part in it).
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+// D = A (16x32 s8, rows) x B (32x8 s8, columns) + D, int32 accumulate.
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D = A (16x16 f16) x B (16x8 f16) + D, fp32 accumulate.
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+#ifdef LEMOQ_TILE_PROFILE
+// development build only: global-timer stamps inside the phases of layer 1 (block 0, thread 0)
+#define SUBSTAMP(idx)                                                                 \
+    do {                                                                              \
+        if (p.stamps != nullptr && l == 1 && blockIdx.x == 0 && threadIdx.x == 0) {   \
+            p.stamps[6 * p.layers + 2 + ph * 8 + (idx)] = clock64();                  \
+        }                                                                             \
+    } while (0)
+#else
+#define SUBSTAMP(idx) \
+    do {              \
+    } while (0)
+#endif
+
+__device__ __forceinline__ void stamp(const MegaParams& p, int slot) {
+    if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.stamps[slot] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// activations as digit planes
+// ---------------------------------------------------------------------------------------------
+// Four activations (fp32 holding fp16-representable values) -> one packed word per plane.  `inv` is the
+// exact power-of-two reciprocal of the group scale.  X = round(f * inv) (|X| < 2^20) is split in two's
+// complement: X = d2 * 2^14 + d1 * 2^7 + d0 with d0, d1 in [0, 127] and d2 in [-64, 63].
+__device__ __forceinline__ void quantise4(const float (&f)[4], float inv, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
+    uint32_t X[4], Y[4], Z[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        // round to nearest even through the 1.5 * 2^23 offset: the integer sits in the low mantissa bits
+        X[j] = __float_as_uint(fmaf(f[j], inv, 12582912.0f)) - 0x4B400000u;
+        Y[j] = X[j] >> 7;
+        Z[j] = static_cast<uint32_t>(static_cast<int>(X[j]) >> 14);
+    }
+    w0 = __byte_perm(__byte_perm(X[0], X[1], 0x0040), __byte_perm(X[2], X[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    w1 = __byte_perm(__byte_perm(Y[0], Y[1], 0x0040), __byte_perm(Y[2], Y[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    w2 = __byte_perm(__byte_perm(Z[0], Z[1], 0x0040), __byte_perm(Z[2], Z[3], 0x0040), 0x5410);
+}
+// Group scale sx = 2^(floor(log2(amax)) - 19) (a fixed tiny scale for a zero group) and its reciprocal.
+__device__ __forceinline__ void group_scale(float amax, float& sx, float& inv) {
+    const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);  // biased exponent
+    if (amax > 0.f && e > 20) {
+        sx = __uint_as_float(static_cast<uint32_t>(e - 19) << 23);
+        inv = __uint_as_float(static_cast<uint32_t>(254 - (e - 19)) << 23);
+    } else {  // zero or denormal-range group: fixed tiny scale keeps the arithmetic exact
+        sx = __uint_as_float(static_cast<uint32_t>(2) << 23);
+        inv = __uint_as_float(static_cast<uint32_t>(252) << 23);
+    }
+}
+// Maximum over the 16 lanes of a half warp (both halves at once).
+__device__ __forceinline__ float half_warp_max(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// One group of 128 values, eight per lane of a half warp (fp32 holding fp16-representable values), of vector
+// element range [k0, k0 + 128) into the plane segments at `planes`: segment (half * 3 + plane) of K/2 + 64 bytes
+// each.  `on` = this half warp has a group at all (the shuffles are executed by everyone).  Returns the group scale.
+__device__ __forceinline__ float store_group_planes(const float (&f)[8], unsigned char* planes, int K, int k0, int lane16, bool on) {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    amax = half_warp_max(amax);
+    float s, inv;
+    group_scale(amax, s, inv);
+    const float lo[4] = {f[0], f[1], f[2], f[3]}, hi[4] = {f[4], f[5], f[6], f[7]};
+    uint2 w0, w1, w2;
+    quantise4(lo, inv, w0.x, w1.x, w2.x);
+    quantise4(hi, inv, w0.y, w1.y, w2.y);
+    if (on) {
+        const int half_k = K >> 1, seg = half_k + kPad;
+        const int hf = k0 >= half_k ? 1 : 0;
+        unsigned char* base = planes + hf * 3 * seg + (k0 - hf * half_k) + lane16 * 8;
+        *reinterpret_cast<uint2*>(base) = w0;
+        *reinterpret_cast<uint2*>(base + seg) = w1;
+        *reinterpret_cast<uint2*>(base + 2 * seg) = w2;
+    }
+    return s;
+}
+
+// Plane weights of the four accumulator registers of a lane (t = lane & 3; c0/c2 are column 2t, c1/c3 column
+// 2t+1).  one_vector: columns 0-2 for all 16 rows.  Otherwise rows 0-7 use columns 0-2, rows 8-15 columns 3-5.
+__device__ __forceinline__ void plane_weights(int t, bool one_vector, float (&pw)[4]) {
+    pw[0] = t == 0 ? 1.f : (t == 1 ? 16384.f : 0.f);
+    pw[1] = t == 0 ? 128.f : 0.f;
+    if (one_vector) {
+        pw[2] = pw[0];
+        pw[3] = pw[1];
+    } else {
+        pw[2] = t == 2 ? 128.f : 0.f;
+        pw[3] = t == 1 ? 1.f : (t == 2 ? 16384.f : 0.f);
+    }
+}
+
+// NB group steps (128 codes of both half rows each) of an int8 tile with NB independent accumulator sets: the
+// tensor-core instruction has a long latency, so consecutive instructions must not depend on each other.
+template <int NB>
+__device__ __forceinline__ float tile_s8_steps(const unsigned char* alo, const unsigned char* ahi, const unsigned char* bp, const float* sx,
+                                               const __half* sc, int gh, int gs0, const float (&pw)[4], float acc) {
+    int c[NB][4];
+#pragma unroll
+    for (int u = 0; u < NB; ++u) c[u][0] = c[u][1] = c[u][2] = c[u][3] = 0;
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+        uint4 a[NB], b[NB], x[NB];
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+            const int off = (gs0 + u) * 128 + jj * 64;
+            a[u] = *reinterpret_cast<const uint4*>(alo + off);
+            b[u] = *reinterpret_cast<const uint4*>(ahi + off);
+            x[u] = *reinterpret_cast<const uint4*>(bp + off);
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u) mma_s8(c[u], a[u].x, b[u].x, a[u].y, b[u].y, x[u].x, x[u].y);
+#pragma unroll
+        for (int u = 0; u < NB; ++u) mma_s8(c[u], a[u].z, b[u].z, a[u].w, b[u].w, x[u].z, x[u].w);
+    }
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+        const int gs = gs0 + u;
+        const float s_lo = __half2float(sc[gs]) * sx[gs];
+        const float s_hi = __half2float(sc[gh + gs]) * sx[gh + gs];
+        acc = fmaf(fmaf(static_cast<float>(c[u][1]), pw[1], static_cast<float>(c[u][0]) * pw[0]), s_lo, acc);
+        acc = fmaf(fmaf(static_cast<float>(c[u][3]), pw[3], static_cast<float>(c[u][2]) * pw[2]), s_hi, acc);
+    }
+    return acc;
+}
+
+// One int8 tile: 8 rows of K codes in a stage (row stride K) against the plane segments of a vector.
+// bp: this lane's segment pointer (+ t*16 applied here).  sx: the K/128 group scales of the vector.  sc: the
+// K/128 fp16 group scales of row g.  Returns the lane's share of row g (to be added over the 4 lanes of a group).
+__device__ __forceinline__ float tile_s8(const unsigned char* st, int K, int g, int t, const unsigned char* bp, const float* sx,
+                                         const __half* sc, const float (&pw)[4]) {
+    const int half_k = K >> 1, gh = K >> 8;  // bytes per half row, groups per half
+    const unsigned char* alo = st + g * K + t * 16;
+    const unsigned char* ahi = alo + half_k;
+    bp += t * 16;
+    float acc = 0.f;
+    if (gh >= 4) {
+#pragma unroll 1
+        for (int gs0 = 0; gs0 < gh; gs0 += 4) acc = tile_s8_steps<4>(alo, ahi, bp, sx, sc, gh, gs0, pw, acc);
+    } else {
+        acc = tile_s8_steps<2>(alo, ahi, bp, sx, sc, gh, 0, pw, acc);
+    }
+    return acc;
+}
+
+// One fp16 tile: 4 rows of H values (row stride 2H bytes) against the fp16 vector xh, whose quarters sit
+// H/2 + 64 bytes apart.  Instruction row v = quarter (v >> 2), tile row (v & 3); B column n = quarter n.
+// Four independent accumulator sets (see above).  Returns this lane's share of tile row (g & 3) (to be added over
+// the lanes g, g ^ 4 with t = 0, 1).
+__device__ __forceinline__ float tile_f16(const unsigned char* st, int H, int g, int t, const unsigned char* xh) {
+    const int qb = H >> 1;  // bytes of a quarter row
+    const unsigned char* alo = st + (g & 3) * (2 * H) + (g >> 2) * qb + t * 16;
+    const unsigned char* ahi = alo + 2 * qb;
+    const unsigned char* bp = xh + (g & 3) * (qb + kPad) + t * 16;
+    float c[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) c[u][0] = c[u][1] = c[u][2] = c[u][3] = 0.f;
+#pragma unroll 1
+    for (int off = 0; off < qb; off += 256) {
+        uint4 a[4], b[4], x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            a[u] = *reinterpret_cast<const uint4*>(alo + off + u * 64);
+            b[u] = *reinterpret_cast<const uint4*>(ahi + off + u * 64);
+            x[u] = *reinterpret_cast<const uint4*>(bp + off + u * 64);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mma_f16(c[u], a[u].x, b[u].x, a[u].y, b[u].y, x[u].x, x[u].y);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mma_f16(c[u], a[u].z, b[u].z, a[u].w, b[u].w, x[u].z, x[u].w);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[0][i] = (c[0][i] + c[1][i]) + (c[2][i] + c[3][i]);
+    // instruction row g holds quarter g >> 2 (column g >> 2), row g + 8 quarter 2 + (g >> 2)
+    const float lo = g < 4 ? c[0][0] : c[0][1], hi = g < 4 ? c[0][2] : c[0][3];
+    return t == 0 ? lo : (t == 1 ? hi : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------
+// shared-memory layout
+// ---------------------------------------------------------------------------------------------
+struct AttnSm {
+    float wm[kStreamWarps];
+    float wl[kStreamWarps];
+    float wacc[kStreamWarps][kHeadDim];
+    __align__(4) short pq[kStreamWarps][kKvTile];  // 15-bit softmax weights of a warp's tile
+    __align__(16) unsigned char qplanes[3 * kQPlaneStride];
+    __align__(16) uint32_t newk[32];
+    __align__(16) uint32_t newv[32];
+    float qsx;
+    unsigned short newks, newvs;  // fp16 bit patterns of the new row's scales
+};
+
+// Sizes, shifts and this block's place in the grid (all row widths are powers of two between 512 and 2048).
+struct Geo {
+    int H, A, F, E, K, S, V, G, b, layers;
+    int shF4;       // log2(F / 4): gate/up tiles per routed expert
+    int fpair;      // down phase: a tile holds the rows of two routed experts (ffn <= 1024)
+    int ftiles;     // down phase: tiles per block of 8 output rows
+    int f_magic;    // ceil(65536 / ftiles)
+    int f_blocks;   // down phase: blocks of 8 output rows this block owns
+    // attention: the same in every layer of the step
+    int pos;        // position of the new token (clamped into the cache)
+    int nf;         // filled length (clamped)
+    int h, split;   // this block's (head, split) unit
+    int tile0;      // first KV tile of this block's slice
+    int owner;      // the slice contains the new token: this block writes its K/V row
+    int has_unit;   // this block has a unit at all
+    int nt[8];      // tiles of this block per kind (index 6: the lm_head tiles)
+};
+
+constexpr int kXPlaneBytes = 6 * (1024 + kPad);                    // plane segments of one vector of up to 2048 values
+constexpr int kBigPlaneBytes = 6 * 4096 + 16 * 6 * kPad;            // plane segments of the routed experts' activations (<= 8192 values in <= 16 vectors)
+constexpr int kBigBytes = kBigPlaneBytes + 64 * 4;                  // + their group scales
+struct Smem {
+    __align__(128) unsigned char ring[kStreamWarps * kStageBytes];
+    __align__(8) unsigned long long full_bars[kStreamWarps];   // a tile has landed in the stage
+    __align__(8) unsigned long long empty_bars[kStreamWarps];  // the consumer is done with the stage
+    volatile int ready_layer;                                  // the routing of layers <= this is in route_id
+    __align__(128) unsigned char xplanes[kXPlaneBytes];
+    float xsx[16];
+    __align__(128) unsigned char xh[4 * (1024 + kPad)];  // fp16 copy of the normalised vector, in quarters (router rows)
+    __align__(128) unsigned char big[kBigBytes > static_cast<int>(sizeof(AttnSm)) ? kBigBytes : static_cast<int>(sizeof(AttnSm))];
+    float part[kPartFloats];
+    float red[64];
+    float cs[2 * kHeadDim];
+    int route_id[32];
+    float route_w[32];
+    Geo geo;
+    MegaLayer layers[kMaxLayers];
+};
+
+__device__ __forceinline__ int udiv_small(int q, int magic) { return (q * magic) >> 16; }  // q / d for q < 65536 / d, magic = ceil(65536 / d)
+
+// ---------------------------------------------------------------------------------------------
+// per-warp tile stream
+// ---------------------------------------------------------------------------------------------
+// The bulk copies of tile (layer, kind, lt) of this block into a stage (a few large copies: starting a copy costs
+// a warp some hundred cycles).  Global tile index of local tile lt: b + lt * G (down phase: row block b + j * G with
+// the top_k routed experts as consecutive tiles).
+__device__ __noinline__ void issue_tile(const Smem& S, int layer, int kind, int lt, uint32_t stage, uint32_t bar) {
+    const Geo& geo = S.geo;
+    const MegaLayer& L = S.layers[layer];
+    const int lane = threadIdx.x & 31;
+    const char* src = nullptr;
+    uint32_t bytes = 0, dst = 0, tx = 0;
+    if (kind == KB) {  // cached positions of this block's head: key codes and value codes (the consumer reads the scales itself)
+        const int first = (geo.tile0 + lt) * kKvTile;
+        const uint32_t npos = static_cast<uint32_t>(min(kKvTile, geo.S - first));  // the last tile of a head may be short
+        const uint32_t p0 = static_cast<uint32_t>(geo.h * geo.S + first);
+        tx = 2 * npos * kHeadDim;
+        if (lane < 2) {
+            src = reinterpret_cast<const char*>(lane == 0 ? L.kc : L.vc) + static_cast<size_t>(p0) * kHeadDim;
+            bytes = npos * kHeadDim;
+            dst = lane * kKvTile * kHeadDim;
+        }
+    } else if (kind == KD) {  // 4 router rows (fp16) in one copy; fewer than 4 experts left: only those
+        const int row0 = (geo.b + lt * geo.G) * 4;
+        const uint32_t nrows = static_cast<uint32_t>(min(4, geo.E - row0));
+        tx = nrows * 2 * geo.H;
+        if (lane == 0) {
+            src = reinterpret_cast<const char*>(L.router) + static_cast<size_t>(row0) * 2 * geo.H;
+            bytes = tx;
+        }
+    } else {
+        // rows of a tile are consecutive in memory (gate/up: two runs of 4): lane 0 (and 1) copy the codes, lane 2 (and 3) the scales
+        const int tg = geo.b + lt * geo.G;
+        uint32_t K = geo.H, row0;    // row width, first row of this lane's run
+        uint32_t rows = 8, at = 0;   // rows of this lane's run and where they land (in rows)
+        bool two = false;            // the tile has a second run (lanes 1 and 3)
+        const char* cbase;
+        const char* sbase;
+        if (kind == KE) {  // 4 gate rows + 4 up rows of one routed expert
+            const int slot = tg >> geo.shF4, n0 = (tg - (slot << geo.shF4)) * 4;
+            row0 = static_cast<uint32_t>(S.route_id[slot]) * 2 * geo.F + n0 + (lane & 1 ? geo.F : 0);
+            rows = 4;
+            at = (lane & 1) * 4;
+            two = true;
+            cbase = reinterpret_cast<const char*>(L.gu_codes);
+            sbase = reinterpret_cast<const char*>(L.gu_scale);
+        } else if (kind == KF) {  // 8 down rows of one routed expert, or of two (odd lanes: the second one)
+            const int j = udiv_small(lt, geo.f_magic), pp = lt - j * geo.ftiles;
+            const int slot = geo.fpair ? 2 * pp + (lane & 1) : pp;
+            two = geo.fpair && 2 * pp + 1 < geo.K;
+            row0 = static_cast<uint32_t>(S.route_id[min(slot, geo.K - 1)]) * geo.H + (geo.b + j * geo.G) * 8;
+            at = geo.fpair ? (lane & 1) * 8 : 0;
+            K = geo.F;
+            cbase = reinterpret_cast<const char*>(L.dn_codes);
+            sbase = reinterpret_cast<const char*>(L.dn_scale);
+        } else {  // 8 consecutive rows of q.k.v / lm_head (KA) or o_proj (KC)
+            row0 = tg * 8;
+            K = kind == KA ? geo.H : geo.A;
+            cbase = reinterpret_cast<const char*>(kind == KA ? L.qkv_codes : L.o_codes);
+            sbase = reinterpret_cast<const char*>(kind == KA ? L.qkv_scale : L.o_scale);
+        }
+        const uint32_t sb = (K >> 7) * 2;  // bytes of one row of group scales
+        tx = (kind == KF && two ? 16u : 8u) * (K + sb);
+        if (lane == 0 || (lane == 1 && two)) {
+            src = cbase + static_cast<size_t>(row0) * K;
+            bytes = rows * K;
+            dst = at * K;
+        } else if (lane == 2 || (lane == 3 && two)) {
+            src = sbase + static_cast<size_t>(row0) * sb;
+            bytes = rows * sb;
+            dst = kScaleOff + at * sb;
+        }
+    }
+    if (lane == 0) mbar_expect_tx(bar, tx);
+    __syncwarp();
+    if (bytes != 0) bulk_g2s(stage + dst, src, bytes, bar);
+}
+
+// Place in the block's tile sequence of the tiles that go through one stage.  The tiles of a block form one
+// sequence over all phases of the step; tile q of the sequence goes through stage q mod 10 and is consumed by warp
+// q mod 10, so the stages that free up first in a phase take the tiles that are needed first in the next one.
+struct Cursor {
+    int layer, kind, lt;  // next tile of the stage
+    int base;             // place of the first tile of (layer, kind) in the sequence, modulo the stages
+    __device__ __forceinline__ void start(const Geo& geo, int stage) {
+        layer = 0;
+        kind = KA;
+        base = 0;
+        lt = stage;
+        normalise(geo, stage);
+    }
+    __device__ __forceinline__ void normalise(const Geo& geo, int stage) {
+        while (kind != KEND) {
+            const int n = layer == geo.layers ? (kind == KA ? geo.nt[6] : 0) : geo.nt[kind];
+            if (lt < n) return;
+            base = (base + n) % kStreamWarps;
+            lt = stage - base + (stage < base ? kStreamWarps : 0);
+            if (layer == geo.layers) {
+                kind = KEND;
+                return;
+            }
+            if (kind == KF) {
+                kind = KA;
+                ++layer;
+            } else {
+                ++kind;
+            }
+        }
+    }
+};
+
+// A producer warp: fills its two stages in sequence order for the whole step.  A stage is refilled as soon as its
+// consumer gives it back, whatever phase the consumers are in; only the expert tiles wait for the routing of
+// their layer.  Every wait is bounded: a producer that gives up raises the flag word and stops, and the consumers
+// then run into their own bounded waits.
+__device__ __noinline__ void producer_loop(Smem& S, int* err_flag, int first_stage) {
+    const Geo& geo = S.geo;
+    const int lane = threadIdx.x & 31;
+    Cursor c0, c1;
+    c0.start(geo, first_stage);
+    c1.start(geo, first_stage + 1);
+    uint32_t used0 = 0, used1 = 0;  // fills of each stage so far
+    bool ok = true;
+#pragma unroll 1
+    while (ok && (c0.kind != KEND || c1.kind != KEND)) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            Cursor& c = i == 0 ? c0 : c1;
+            uint32_t& used = i == 0 ? used0 : used1;
+            if (!ok || c.kind == KEND) continue;
+            const int stage = first_stage + i;
+            if (c.kind >= KE) {  // expert tiles: the routing of the layer must be known
+                uint32_t n = 0;
+                while (S.ready_layer < c.layer) {
+                    __nanosleep(64);
+                    if (++n > (1u << 22)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                __threadfence_block();
+            }
+            if (ok && used > 0) ok = mbar_wait(smem_u32(&S.empty_bars[stage]), (used - 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            issue_tile(S, c.layer, c.kind, c.lt, smem_u32(S.ring) + static_cast<uint32_t>(stage) * kStageBytes, smem_u32(&S.full_bars[stage]));
+            ++used;
+            c.lt += kStreamWarps;
+            c.normalise(geo, stage);
+        }
+    }
+    if (!ok && err_flag && lane == 0) atomicOr(err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+}
+
+// Consumer side of a stage: wait for the tile (warp-uniform result; false on time-out), give the stage back.
+__device__ __forceinline__ bool stage_acquire(uint32_t full_bar, uint32_t parity, int* err_flag) {
+    bool ok = mbar_wait(full_bar, parity);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && err_flag && (threadIdx.x & 31) == 0) atomicOr(err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+    return ok;
+}
+__device__ __forceinline__ void stage_release(uint32_t empty_bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// routing: softmax + top-k of the E fp16 logits (E <= 128) by one warp.  Probabilities are positive
+// floats, so their bit patterns order like unsigned integers: a warp-wide integer maximum plus a ballot
+// gives the largest probability and its lowest index per round.
+// ---------------------------------------------------------------------------------------------
+template <int PER>  // experts per lane: 2 for E <= 64, 4 for E <= 128
+__device__ __forceinline__ void warp_topk_per(const __half* __restrict__ logits, int E, int K, bool norm, int lane, int& id_reg, float& w_reg) {
+    float v[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? __half2float(__ldcg(logits + e)) : -INFINITY;
+        mx = fmaxf(mx, v[j]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? expf(v[j] - mx) : 0.f;
+        sum += v[j];
+    }
+    sum = warp_sum(sum);
+    unsigned int key[PER];  // bits of the probability + 1; 0 = absent or already taken
+#pragma unroll
+    for (int j = 0; j < PER; ++j) key[j] = (lane + 32 * j) < E ? __float_as_uint(v[j] / sum) + 1u : 0u;
+    float wsum = 0.f;
+    id_reg = 0;
+    w_reg = 0.f;
+#pragma unroll 1
+    for (int k = 0; k < K; ++k) {
+        unsigned int own = key[0];
+#pragma unroll
+        for (int j = 1; j < PER; ++j) own = max(own, key[j]);
+        const unsigned int top = __reduce_max_sync(0xffffffffu, own);
+        int bi = -1;
+#pragma unroll
+        for (int j = PER - 1; j >= 0; --j) {
+            const unsigned int b = __ballot_sync(0xffffffffu, key[j] == top);
+            if (b) bi = 32 * j + __ffs(b) - 1;
+        }
+        const float best = __uint_as_float(top - 1u);
+        wsum += best;
+        if (lane == k) {
+            id_reg = bi;
+            w_reg = best;
+        }
+        if ((bi & 31) == lane) {
+#pragma unroll
+            for (int j = 0; j < PER; ++j)
+                if (j == (bi >> 5)) key[j] = 0u;
+        }
+    }
+    if (norm) w_reg = w_reg / wsum;
+    w_reg = __half2float(__float2half_rn(w_reg));  // the routing weights are used in fp16
+}
+__device__ __noinline__ void warp_topk(const __half* __restrict__ logits, int E, int K, bool norm, int lane, int& id_reg, float& w_reg) {
+    if (E <= 64) warp_topk_per<2>(logits, E, K, norm, lane, id_reg, w_reg);
+    else warp_topk_per<4>(logits, E, K, norm, lane, id_reg, w_reg);
+}
+
+// ---------------------------------------------------------------------------------------------
+// block-wide preparation of a phase's activation vectors
+// ---------------------------------------------------------------------------------------------
+// ngroups groups of 128 fp16 values (contiguous at src; vectors of K values each) -> plane segments (vector v at
+// planes + v * 6 * (K/2 + 64)) and group scales sx[group].  With nw (one vector of at most 2048 values) the values
+// are RMS-normalised first; xh, when given, receives them as fp16 in quarters.  A half warp handles a group (eight
+// values per lane), the block twenty groups per pass; the next pass's values are requested before the current
+// ones are worked on.
+__device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, const __half* __restrict__ nw, int K, int ngroups,
+                                     unsigned char* planes, float* sx, unsigned char* xh, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, lane16 = lane & 15;
+    constexpr int kPerPass = 2 * kStreamWarps;
+    int gi = warp * 2 + (lane >> 4);
+    uint4 cur = gi < ngroups ? ld_cg16(src + gi * 128 + lane16 * 8) : make_uint4(0u, 0u, 0u, 0u);
+    uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+    float rstd = 0.f;
+    if (nw != nullptr) {  // one pass: at most 16 groups
+        if (gi < ngroups) wv = *reinterpret_cast<const uint4*>(nw + gi * 128 + lane16 * 8);
+        float xf[8];
+        unpack8_h(cur, xf);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(xf[j], xf[j], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        consumer_sync();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kStreamWarps; ++w) tot += red[w];
+        rstd = 1.0f / sqrtf(tot / static_cast<float>(K) + eps);
+    }
+    const int kshift = 31 - __clz(K);
+#pragma unroll 1
+    for (int g0 = 0; g0 < ngroups; g0 += kPerPass, gi += kPerPass) {
+        const uint4 nxt = gi + kPerPass < ngroups ? ld_cg16(src + (gi + kPerPass) * 128 + lane16 * 8) : make_uint4(0u, 0u, 0u, 0u);
+        const __half* xv = reinterpret_cast<const __half*>(&cur);
+        const __half* wh = reinterpret_cast<const __half*>(&wv);
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = nw != nullptr ? norm_elem(xv[j], rstd, wh[j]) : __half2float(xv[j]);
+        const bool on = gi < ngroups;
+        const int v = (gi * 128) >> kshift, k0 = gi * 128 - (v << kshift);
+        const float s = store_group_planes(f, planes + v * 6 * ((K >> 1) + kPad), K, k0, lane16, on);
+        if (on && lane16 == 0) sx[gi] = s;
+        if (xh != nullptr && on) {
+            uint4 o;
+            __half2 h;
+            h = __floats2half2_rn(f[0], f[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(f[2], f[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(f[4], f[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(f[6], f[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+            const int qv = K >> 2, q = k0 >> (kshift - 2);  // values per quarter, quarter of this group
+            *reinterpret_cast<uint4*>(xh + q * (2 * qv + kPad) + (k0 - q * qv) * 2 + lane16 * 16) = o;
+        }
+        cur = nxt;
+    }
+    consumer_sync();
+}
+
+// The attention output as the o_proj input: a half warp merges the splits of one head (partials (m, l, acc[128]) of
+// the (head, split) units, taken four splits at a time in split order), rounds to fp16 and builds the planes of the
+// head's group.  Lane i of the half warp holds dimensions 8i .. 8i+7.
+__device__ __noinline__ void prepare_attention_output(const MegaParams& p, Smem& S) {
+    constexpr int D = kHeadDim;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, lane16 = lane & 15;
+    const int head = warp * 2 + (lane >> 4);
+    const bool on = head < p.heads;
+    const int hd = on ? head : 0;
+    const float* hacc = p.attn_part + static_cast<int64_t>(hd) * p.splits * D + lane16 * 8;
+    const float* hml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + static_cast<int64_t>(hd) * p.splits * 2;
+    float big = -INFINITY, den = 0.f;
+    float num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int j0 = 0; j0 < p.splits; j0 += 4) {
+        float4 a0[4], a1[4];
+        float2 mv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j0 + j < p.splits) {
+                a0[j] = __ldcg(reinterpret_cast<const float4*>(hacc + (j0 + j) * D));
+                a1[j] = __ldcg(reinterpret_cast<const float4*>(hacc + (j0 + j) * D + 4));
+                mv[j] = __ldcg(reinterpret_cast<const float2*>(hml + 2 * (j0 + j)));
+            } else {
+                a0[j] = a1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                mv[j] = make_float2(-INFINITY, 0.f);
+            }
+        }
+        float nb = big;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) nb = fmaxf(nb, mv[j].x);
+        const float ref = nb > -INFINITY ? nb : 0.f;
+        const float keep = exp2f(big - ref);  // 0 for the first batch (big = -inf)
+        den *= keep;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) num[i] *= keep;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float w = exp2f(mv[j].x - ref);
+            den = fmaf(mv[j].y, w, den);
+            num[0] = fmaf(a0[j].x, w, num[0]);
+            num[1] = fmaf(a0[j].y, w, num[1]);
+            num[2] = fmaf(a0[j].z, w, num[2]);
+            num[3] = fmaf(a0[j].w, w, num[3]);
+            num[4] = fmaf(a1[j].x, w, num[4]);
+            num[5] = fmaf(a1[j].y, w, num[5]);
+            num[6] = fmaf(a1[j].z, w, num[6]);
+            num[7] = fmaf(a1[j].w, w, num[7]);
+        }
+        big = nb;
+    }
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __half2float(__float2half_rn(den > 0.f ? num[j] / den : num[j]));
+    const float s = store_group_planes(f, S.xplanes, p.heads * D, hd * D, lane16, on);
+    if (on && lane16 == 0) S.xsx[hd] = s;
+    consumer_sync();
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention phase (one (head, split) unit per block; head_dim 128, int8 KV with per-token scales)
+// ---------------------------------------------------------------------------------------------
+// Warp 0: q (RMSNorm over all heads, RoPE, softmax scale, digit planes).  Warp 1 / warp 2 of the block that owns
+// the new position: the new K row (norm, RoPE) / V row into the fp16 cache and, quantised, into the int8 mirror
+// and shared memory.  Lane i holds dimensions 4i .. 4i+3; the RoPE partner (d +- 64) lives 16 lanes away.
+__device__ __noinline__ void attention_prologue(const MegaParams& p, const MegaLayer& L, Smem& S) {
+    constexpr int D = kHeadDim;
+    AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
+    const Geo& geo = S.geo;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp == 0 || (geo.owner && warp < 3)) {
+        const int A = geo.A, h = geo.h;
+        const uint2 raw = ld_cg8(p.qkv + warp * A + h * D + lane * 4);
+        const __half* rh = reinterpret_cast<const __half*>(&raw);
+        float f[4];
+        if (warp < 2) {
+            const uint2 wv = *reinterpret_cast<const uint2*>((warp == 0 ? L.q_norm : L.k_norm) + h * D + lane * 4);
+            const __half* wh = reinterpret_cast<const __half*>(&wv);
+            // sum of squares of the whole q (k) row: one partial per block of the grid, added in a fixed order
+            float s = 0.f;
+            for (int b = lane; b < geo.G; b += 32) s += __ldcg(p.stats + warp * geo.G + b);
+            s = warp_sum(s);
+            const float rstd = 1.0f / sqrtf(s / static_cast<float>(A) + p.eps);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float x = norm_elem(rh[j], rstd, wh[j]);
+                const float o = __shfl_xor_sync(0xffffffffu, x, 16);
+                const float rot = lane < 16 ? -o : o;
+                f[j] = __half2float(__float2half_rn(__fadd_rn(__fmul_rn(x, S.cs[4 * lane + j]), __fmul_rn(rot, S.cs[D + 4 * lane + j]))));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = __half2float(rh[j]);
+        }
+        if (warp == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] *= p.qk_scale_log2;
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))));
+            float s, inv;
+            group_scale(amax, s, inv);
+            uint32_t w0, w1, w2;
+            quantise4(f, inv, w0, w1, w2);
+            *reinterpret_cast<uint32_t*>(sm.qplanes + 4 * lane) = w0;
+            *reinterpret_cast<uint32_t*>(sm.qplanes + kQPlaneStride + 4 * lane) = w1;
+            *reinterpret_cast<uint32_t*>(sm.qplanes + 2 * kQPlaneStride + 4 * lane) = w2;
+            if (lane == 0) sm.qsx = s;
+        } else {
+            const int64_t at = (static_cast<int64_t>(h) * geo.S + geo.pos) * D + lane * 4;
+            __half2 h01 = __floats2half2_rn(f[0], f[1]), h23 = __floats2half2_rn(f[2], f[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&h01);
+            o.y = *reinterpret_cast<uint32_t*>(&h23);
+            *reinterpret_cast<uint2*>((warp == 1 ? L.keys : L.values) + at) = o;
+            const float amax = warp_max(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))));
+            const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = static_cast<int>(fminf(fmaxf(rintf(__fdiv_rn(f[j], sc)), -127.0f), 127.0f));
+                packed |= (static_cast<uint32_t>(c) & 0xffu) << (8 * j);
+            }
+            *reinterpret_cast<uint32_t*>((warp == 1 ? L.kc : L.vc) + at) = packed;
+            (warp == 1 ? sm.newk : sm.newv)[lane] = packed;
+            if (lane == 0) {
+                const __half hs = __float2half_rn(sc);
+                (warp == 1 ? L.ks : L.vs)[static_cast<int64_t>(h) * geo.S + geo.pos] = hs;
+                (warp == 1 ? sm.newks : sm.newvs) = __half_as_ushort(hs);
+            }
+        }
+    }
+    consumer_sync();
+}
+
+// One KV tile (64 positions in a stage) of the warp: scores through the int8 dot product against the planes of q
+// (instruction rows = positions), online softmax (base 2), values with each lane owning four output dimensions.
+__device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, const Geo& geo, int lt, int lane, int warp, const float (&pw)[4],
+                                               const float (&kscale)[2], const float (&vscale)[2], float& m_i, float& l_i, float (&acc)[4]) {
+    constexpr int D = kHeadDim, T = kKvTile;
+    const int g = lane >> 2, t = lane & 3;
+    const int base = (geo.tile0 + lt) * T;
+    const int nvalid = min(T, geo.nf - base);
+    if (geo.owner && geo.pos >= base && geo.pos < base + T) {
+        // the row of the new token: the codes this block has just derived (the copy may have read the slot before the write)
+        const int row = geo.pos - base;
+        reinterpret_cast<uint32_t*>(st + row * D)[lane] = sm.newk[lane];
+        reinterpret_cast<uint32_t*>(st + T * D + row * D)[lane] = sm.newv[lane];
+        __syncwarp();
+    }
+    // kscale[r] / vscale[r] of this lane belong to position 32 r + lane of the tile
+    auto scale_of = [&](const float (&sc)[2], int pi) { return __shfl_sync(0xffffffffu, pi < 32 ? sc[0] : sc[1], pi & 31); };
+    const unsigned char* qp = sm.qplanes + (g < 3 ? g : (g & 1)) * kQPlaneStride + t * 16;
+    const float qsx = sm.qsx;
+    float s[T / 8];
+#pragma unroll
+    for (int blk = 0; blk < T / 16; ++blk) {
+        int c[4] = {0, 0, 0, 0};
+        const unsigned char* alo = st + (blk * 16 + g) * D + t * 16;
+        const unsigned char* ahi = alo + 8 * D;
+#pragma unroll
+        for (int jd = 0; jd < 2; ++jd) {
+            const uint4 a = *reinterpret_cast<const uint4*>(alo + jd * 64);
+            const uint4 b = *reinterpret_cast<const uint4*>(ahi + jd * 64);
+            const uint4 x = *reinterpret_cast<const uint4*>(qp + jd * 64);
+            mma_s8(c, a.x, b.x, a.y, b.y, x.x, x.y);
+            mma_s8(c, a.z, b.z, a.w, b.w, x.z, x.w);
+        }
+        float vlo = fmaf(static_cast<float>(c[1]), pw[1], static_cast<float>(c[0]) * pw[0]);
+        float vhi = fmaf(static_cast<float>(c[3]), pw[3], static_cast<float>(c[2]) * pw[2]);
+        vlo += __shfl_xor_sync(0xffffffffu, vlo, 1);
+        vhi += __shfl_xor_sync(0xffffffffu, vhi, 1);
+        vlo += __shfl_xor_sync(0xffffffffu, vlo, 2);
+        vhi += __shfl_xor_sync(0xffffffffu, vhi, 2);
+        const int plo = blk * 16 + g, phi = plo + 8;
+        const float klo = scale_of(kscale, plo), khi = scale_of(kscale, phi);
+        s[2 * blk] = plo < nvalid ? vlo * qsx * klo : -INFINITY;
+        s[2 * blk + 1] = phi < nvalid ? vhi * qsx * khi : -INFINITY;
+    }
+    float mx = s[0];
+#pragma unroll
+    for (int i = 1; i < T / 8; ++i) mx = fmaxf(mx, s[i]);
+    const float m_new = fmaxf(m_i, warp_max(mx));  // finite: position 0 of the tile is valid
+    const float alpha = exp2f(m_i - m_new);
+    float lsum = 0.f;
+#pragma unroll
+    for (int i = 0; i < T / 8; ++i) {
+        s[i] = s[i] > -INFINITY ? exp2f(s[i] - m_new) : 0.f;
+        lsum += s[i];
+    }
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 4);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 8);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 16);
+    l_i = fmaf(l_i, alpha, lsum);
+    m_i = m_new;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] *= alpha;
+    // values: the weights w_j = p_j * vscale_j of the tile as 15-bit integers (relative to the tile's largest), two
+    // positions per word; a lane owns four output dimensions and takes the positions in pairs: two byte permutes put
+    // the codes of a pair next to each other, four 2-way integer dot products add both positions to the four sums
+    float wj[T / 8], wmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < T / 8; ++i) {
+        const int pi = (i >> 1) * 16 + g + (i & 1) * 8;
+        const float vsc = scale_of(vscale, pi);
+        wj[i] = pi < nvalid ? s[i] * vsc : 0.f;
+        wmax = fmaxf(wmax, wj[i]);
+    }
+    wmax = warp_max(wmax);
+    const float qs = wmax > 0.f ? 32767.0f / wmax : 0.f;
+    __syncwarp();
+    if (t == 0) {
+#pragma unroll
+        for (int i = 0; i < T / 8; ++i) {
+            const int pi = (i >> 1) * 16 + g + (i & 1) * 8;
+            sm.pq[warp][pi] = static_cast<short>(__float2int_rn(wj[i] * qs));
+        }
+    }
+    __syncwarp();
+    const unsigned char* vrow = st + T * D + lane * 4;
+    const uint32_t* pq = reinterpret_cast<const uint32_t*>(sm.pq[warp]);
+    int ai[4] = {0, 0, 0, 0};
+#pragma unroll 4
+    for (int j2 = 0; j2 < T / 2; ++j2) {
+        const int pp = static_cast<int>(pq[j2]);
+        const uint32_t v0 = *reinterpret_cast<const uint32_t*>(vrow + (2 * j2) * D);
+        const uint32_t v1 = *reinterpret_cast<const uint32_t*>(vrow + (2 * j2 + 1) * D);
+        const int w01 = static_cast<int>(__byte_perm(v0, v1, 0x5140));  // dimension 0 of both positions, then dimension 1
+        const int w23 = static_cast<int>(__byte_perm(v0, v1, 0x7362));  // dimension 2 of both positions, then dimension 3
+        ai[0] = __dp2a_lo(pp, w01, ai[0]);
+        ai[1] = __dp2a_hi(pp, w01, ai[1]);
+        ai[2] = __dp2a_lo(pp, w23, ai[2]);
+        ai[3] = __dp2a_hi(pp, w23, ai[3]);
+    }
+    const float back = wmax * (1.0f / 32767.0f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = fmaf(static_cast<float>(ai[j]), back, acc[j]);
+}
+
+// Merge of the block's warps into the unit's partial (m, l, acc[128]).
+__device__ __noinline__ void attention_partial(const MegaParams& p, Smem& S) {
+    constexpr int D = kHeadDim;
+    AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
+    const Geo& geo = S.geo;
+    const int tid = threadIdx.x;
+    // partial layout: acc[(h*splits + split)*D + d], then the (m, l) pairs
+    if (tid < D) {
+        constexpr int nactive = kStreamWarps;  // warps without a tile hold (-inf, 0, 0)
+        float big = -INFINITY;
+#pragma unroll 1
+        for (int w = 0; w < nactive; ++w) big = fmaxf(big, sm.wm[w]);
+        const float bs = big > -INFINITY ? big : 0.f;
+        float a = 0.f, l = 0.f;
+#pragma unroll 1
+        for (int w = 0; w < nactive; ++w) {
+            const float wt = exp2f(sm.wm[w] - bs);
+            a = fmaf(sm.wacc[w][tid], wt, a);
+            l = fmaf(sm.wl[w], wt, l);
+        }
+        p.attn_part[(static_cast<int64_t>(geo.h) * p.splits + geo.split) * D + tid] = a;
+        if (tid == 0) {
+            float* ml = p.attn_part + static_cast<int64_t>(p.heads) * p.splits * D + (static_cast<int64_t>(geo.h) * p.splits + geo.split) * 2;
+            ml[0] = big;
+            ml[1] = l;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int count_of(int n, int b, int G) { return n > b ? (n - b + G - 1) / G : 0; }
+__device__ __forceinline__ int log2i(int v) { return 31 - __clz(v); }
+
+// greedy pick: is candidate (v, i) better than (best, bi)?  NaN counts as the largest value (the rule of a
+// host arg-max), the lowest index wins ties.
+__device__ __noinline__ bool better(float v, int i, float best, int bi) {
+    const bool vn = v != v, bn = best != best;
+    if (vn != bn) return vn;
+    if (vn) return i < bi;
+    return v > best || (v == best && i < bi);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_constant__ MegaParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = gridDim.x, b = blockIdx.x;
+    const int A = p.heads * p.D;
+    {
+        const uint64_t* src = reinterpret_cast<const uint64_t*>(p.L);
+        uint64_t* dst = reinterpret_cast<uint64_t*>(S.layers);
+        const int words = (p.layers + 1) * static_cast<int>(sizeof(MegaLayer) / 8);
+        for (int i = tid; i < words; i += kThreads) dst[i] = src[i];
+    }
+
+    // Position, cache slice, RoPE row and the tile counts are the same in every layer of the step.
+    int64_t tok = *p.token;
+    {
+        int nf = *p.filled;
+        int64_t pos = *p.cache_position;
+        if (nf < 0 || nf > p.S) {
+            if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_LENGTH);
+            nf = nf < 0 ? 0 : p.S;
+        }
+        const bool pos_ok = pos >= 0 && pos < p.S;
+        if (!pos_ok) {
+            if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_POSITION);
+            pos = pos < 0 ? 0 : p.S - 1;
+        }
+        if (tok < 0 || tok >= p.V) {
+            if (p.err_flag && tid == 0) atomicOr(p.err_flag, LEMOQ_FLAG_BAD_TOKEN);
+            tok = tok < 0 ? 0 : p.V - 1;
+        }
+        if (tid == 0) {
+            Geo& geo = S.geo;
+            geo.H = p.H; geo.A = A; geo.F = p.F; geo.E = p.E; geo.K = p.K; geo.S = p.S; geo.V = p.V; geo.G = G; geo.b = b;
+            geo.layers = p.layers;
+            geo.shF4 = log2i(p.F >> 2);
+            geo.fpair = p.F <= 1024 && p.K >= 2;
+            geo.ftiles = geo.fpair ? (p.K + 1) / 2 : p.K;
+            geo.f_magic = (65536 + geo.ftiles - 1) / geo.ftiles;
+            geo.f_blocks = count_of(p.H / 8, b, G);
+            const bool has_unit = b < p.heads * p.splits;
+            const int unit = has_unit ? b : 0;
+            const int ntile_total = (nf + kKvTile - 1) / kKvTile;
+            const int tps = (ntile_total + p.splits - 1) / p.splits;
+            geo.h = unit / p.splits;
+            geo.split = unit - geo.h * p.splits;
+            geo.pos = static_cast<int>(pos);
+            geo.nf = nf;
+            geo.has_unit = has_unit ? 1 : 0;
+            geo.tile0 = geo.split * tps;
+            const int tile1 = min(geo.tile0 + tps, ntile_total);
+            const int ptile = static_cast<int>(pos) / kKvTile;
+            geo.owner = has_unit && pos_ok && pos < nf && ptile >= geo.tile0 && ptile < tile1;
+            geo.nt[KA] = count_of(3 * A / 8, b, G);
+            geo.nt[KB] = has_unit && tile1 > geo.tile0 ? tile1 - geo.tile0 : 0;
+            geo.nt[KC] = count_of(p.H / 8, b, G);
+            geo.nt[KD] = count_of((p.E + 3) / 4, b, G);
+            geo.nt[KE] = count_of(p.K * p.F / 4, b, G);
+            geo.nt[KF] = geo.f_blocks * geo.ftiles;
+            geo.nt[6] = count_of(p.V / 8, b, G);
+            geo.nt[7] = 0;
+        }
+        if (tid < kHeadDim) {
+            S.cs[tid] = __half2float(p.rope_cos[pos * kHeadDim + tid]);
+            S.cs[kHeadDim + tid] = __half2float(p.rope_sin[pos * kHeadDim + tid]);
+        }
+    }
+    if (tid == 0) {
+        for (int st = 0; st < kStreamWarps; ++st) {
+            mbar_init(smem_u32(&S.full_bars[st]), 1u);
+            mbar_init(smem_u32(&S.empty_bars[st]), 1u);
+        }
+        mbar_fence_init();
+        S.ready_layer = -1;
+    }
+    __syncthreads();  // the one barrier of all warps: from here on producers and consumers only meet at the stages
+    if (warp >= kStreamWarps) {
+        producer_loop(S, p.err_flag, 2 * (warp - kStreamWarps));
+        return;
+    }
+    const Geo& geo = S.geo;
+    const uint32_t full_bar = smem_u32(&S.full_bars[warp]), empty_bar = smem_u32(&S.empty_bars[warp]);
+    uint32_t c_par = 0;  // parity of the next tile's arrival in this warp's stage
+    int cbase = 0;  // the same place for the phase being worked on
+    unsigned char* const my_stage = S.ring + static_cast<size_t>(warp) * kStageBytes;
+
+    unsigned int bar_target = ld_acquire_u32(p.bar_epoch) * static_cast<unsigned int>(p.barriers_per_launch) * gridDim.x;
+    stamp(p, 0);
+    const __half* x_prev = p.embed + tok * static_cast<int64_t>(p.H);
+    float pw1v[4], pw2v[4];
+    plane_weights(t, true, pw1v);
+    plane_weights(t, false, pw2v);
+    const int bseg = g < 6 ? g : (g & 1);  // plane segment this lane feeds to B: first half planes 0-2, second half planes 0-2
+    float* const fsx = reinterpret_cast<float*>(S.big + kBigPlaneBytes);  // group scales of the routed experts' activations
+    float pick_v = -INFINITY;
+    int pick_i = 0x7fffffff;
+    int l = 0, ph = 0;  // phase: 0 q.k.v / lm_head, 1 attention, 2 o_proj, 3 router, 4 gate/up, 5 down
+    const int nphases = 6 * p.layers + 1;
+
+#pragma unroll 1
+    for (int step = 0; step <= nphases; ++step) {
+        // ---- grid barrier behind the previous phase --------------------------------------------------------
+        if (step > 0) {
+            if (tid == 0) {
+                unsigned int n = 0;
+                while (static_cast<int>(ld_acquire_u32(p.bar_counter) - bar_target) < 0) {
+                    if (++n > kBarrierSpinLimit) {
+                        if (p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            consumer_sync();
+            stamp(p, step);
+        }
+        if (step == nphases) break;
+        const MegaLayer& L = S.layers[l];
+        const bool last = l == p.layers;
+        const int ntiles = last ? geo.nt[6] : geo.nt[ph];
+        const int lt0 = warp - cbase + (warp < cbase ? kStreamWarps : 0);  // this warp's first tile of the phase
+        cbase = (cbase + ntiles) % kStreamWarps;
+        float sq = 0.f, sk = 0.f;  // phase A: sums of squares of the q / k values this lane stored
+        SUBSTAMP(0);
+
+        if (ph == 1) {
+            if (geo.has_unit) {
+                AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
+                attention_prologue(p, L, S);
+                SUBSTAMP(1);
+                {
+                    float m_i = -INFINITY, l_i = 0.f;
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                    for (int lt = lt0; lt < ntiles; lt += kStreamWarps) {
+                        // the scales of the tile's positions (two per lane), requested before the wait for the codes
+                        float kscale[2], vscale[2];
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const int pos = (geo.tile0 + lt) * kKvTile + 32 * r + lane;
+                            const bool in = pos < geo.nf;
+                            const int64_t at = static_cast<int64_t>(geo.h) * geo.S + (in ? pos : 0);
+                            const bool fresh = geo.owner && pos == geo.pos;  // the new token: the scales this block has just derived
+                            kscale[r] = fresh ? __half2float(__ushort_as_half(sm.newks)) : (in ? __half2float(__ldcg(L.ks + at)) : 0.f);
+                            vscale[r] = fresh ? __half2float(__ushort_as_half(sm.newvs)) : (in ? __half2float(__ldcg(L.vs + at)) : 0.f);
+                        }
+                        if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
+                        c_par ^= 1u;
+                        attention_tile(my_stage, sm, geo, lt, lane, warp, pw1v, kscale, vscale, m_i, l_i, acc);
+                        stage_release(empty_bar);
+                    }
+                    *reinterpret_cast<float4*>(&sm.wacc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    if (lane == 0) {
+                        sm.wm[warp] = m_i;
+                        sm.wl[warp] = l_i;
+                    }
+                }
+                SUBSTAMP(3);
+                consumer_sync();
+                attention_partial(p, S);
+                SUBSTAMP(4);
+            }
+        } else {
+            // ---- block-wide preparation of the phase -----------------------------------------------------
+            if (ph == 4) {
+                if (warp == 0) {  // one warp routes, the others pick the result up from shared memory
+                    int id;
+                    float w;
+                    warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane, id, w);
+                    S.route_id[lane] = id;
+                    S.route_w[lane] = lane < p.K ? w : 0.f;
+                    if (b == 0 && lane < p.K) {
+                        p.top_i[static_cast<int64_t>(l) * p.K + lane] = id;
+                        p.top_w[lane] = __float2half_rn(w);
+                    }
+                }
+                if (warp == 0) {
+                    __threadfence_block();
+                    if (lane == 0) S.ready_layer = l;  // the producers may start the expert tiles of this layer
+                }
+                consumer_sync();
+                SUBSTAMP(2);
+            } else if (ph == 2) {
+                prepare_attention_output(p, S);
+            } else {
+                const int K = ph == 5 ? p.F : p.H;
+                prepare(p.eps, ph == 0 ? x_prev : (ph == 3 ? p.xa : p.act), ph == 0 ? L.ln1 : (ph == 3 ? L.ln2 : nullptr), K,
+                        ph == 5 ? (p.K * p.F) >> 7 : K >> 7, ph == 5 ? S.big : S.xplanes, ph == 5 ? fsx : S.xsx, ph == 3 ? S.xh : nullptr, S.red);
+            }
+            SUBSTAMP(1);
+            // the residual of this thread's down row (in flight while the tiles are worked on)
+            __half resid_f = __float2half_rn(0.f);
+            if (ph == 5 && tid < geo.f_blocks * 8) resid_f = __ldcg(p.xa + (b + (tid >> 3) * G) * 8 + (tid & 7));
+            // ---- this warp's tiles of the phase: a warp finishes the rows of its tile by itself ------------------
+            {
+                const int K = ph == 2 ? A : (ph == 5 ? p.F : p.H);
+#pragma unroll 1
+                for (int lt = lt0; lt < ntiles; lt += kStreamWarps) {
+                    const int tg = b + lt * G;  // global tile index (not in the down phase)
+                    __half resid = __float2half_rn(0.f);
+                    if (ph == 2) resid = __ldcg(x_prev + tg * 8 + g);  // in flight while the tile is worked on
+                    if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
+                    c_par ^= 1u;
+                    float val;
+#ifdef LEMOQ_TILE_PROFILE
+                    const long long tc0 = clock64();
+#endif
+                    if (ph == 3) {
+                        val = tile_f16(my_stage, p.H, g, t, S.xh);
+                        val += __shfl_xor_sync(0xffffffffu, val, 1);
+                        val += __shfl_xor_sync(0xffffffffu, val, 16);
+                    } else if (ph == 5) {
+                        // one or two routed experts' rows of the same 8 outputs: each against its own activation planes
+                        const int j = udiv_small(lt, geo.f_magic), pp = lt - j * geo.ftiles;
+                        const int seg = (K >> 1) + kPad, slot = geo.fpair ? 2 * pp : pp;
+                        const __half* sc = reinterpret_cast<const __half*>(my_stage + kScaleOff) + g * (K >> 7);
+                        val = tile_s8(my_stage, K, g, t, S.big + slot * 6 * seg + bseg * seg, fsx + slot * (K >> 7), sc, pw2v);
+                        val += __shfl_xor_sync(0xffffffffu, val, 1);
+                        val += __shfl_xor_sync(0xffffffffu, val, 2);
+                        if (t == 0) S.part[(j * p.K + slot) * 8 + g] = val;
+                        if (geo.fpair && slot + 1 < p.K) {
+                            val = tile_s8(my_stage + 8 * K, K, g, t, S.big + (slot + 1) * 6 * seg + bseg * seg, fsx + (slot + 1) * (K >> 7),
+                                          sc + 8 * (K >> 7), pw2v);
+                            val += __shfl_xor_sync(0xffffffffu, val, 1);
+                            val += __shfl_xor_sync(0xffffffffu, val, 2);
+                            if (t == 0) S.part[(j * p.K + slot + 1) * 8 + g] = val;
+                        }
+                    } else {
+                        val = tile_s8(my_stage, K, g, t, S.xplanes + bseg * ((K >> 1) + kPad), S.xsx,
+                                      reinterpret_cast<const __half*>(my_stage + kScaleOff) + g * (K >> 7), pw2v);
+                        val += __shfl_xor_sync(0xffffffffu, val, 1);
+                        val += __shfl_xor_sync(0xffffffffu, val, 2);
+                    }
+#ifdef LEMOQ_TILE_PROFILE
+                    if (l == 1 && lane == 0 && p.stamps && val != 1234.5f) {
+                        // per (phase, block < 16): cycles of one tile's arithmetic
+                        if (b < 16) p.stamps[6 * p.layers + 2 + 48 + ph * 16 + b] = static_cast<unsigned long long>(clock64() - tc0);
+                    }
+#endif
+                    stage_release(empty_bar);
+                    if (ph == 0) {
+                        const int n = tg * 8 + g;
+                        const __half hv = __float2half_rn(val);
+                        const float f = __half2float(hv);
+                        if (t == 0) {
+                            if (!last) {
+                                p.qkv[n] = hv;
+                                if (n < A) sq = fmaf(f, f, sq);
+                                else if (n < 2 * A) sk = fmaf(f, f, sk);
+                            } else {
+                                p.logits[n] = hv;
+                                if (better(f, n, pick_v, pick_i)) {
+                                    pick_v = f;
+                                    pick_i = n;
+                                }
+                            }
+                        }
+                    } else if (ph == 2) {
+                        if (t == 0) p.xa[tg * 8 + g] = __hadd(__float2half_rn(val), resid);
+                    } else if (ph == 3) {
+                        const int e = tg * 4 + g;
+                        if (t == 0 && g < 4 && e < p.E) p.router_logits[static_cast<int64_t>(l) * p.E + e] = __float2half_rn(val);
+                    } else if (ph == 4) {
+                        const float up = __shfl_down_sync(0xffffffffu, val, 16);  // rows 4-7 of the tile are the up rows
+                        const int slot = tg >> geo.shF4, n = ((tg - (slot << geo.shF4)) << 2) + g;
+                        if (t == 0 && g < 4) p.act[slot * p.F + n] = __float2half_rn(val * (1.0f / (1.0f + expf(-val))) * up);
+                    }
+                }
+            }
+            SUBSTAMP(3);
+            if (ph == 5) {
+                // the routed experts of a down row are consecutive tiles: routing-weighted sum in slot order
+                const int nrows = geo.f_blocks * 8;
+                __half resid = resid_f;
+                consumer_sync();
+#pragma unroll 1
+                for (int i = tid; i < nrows; i += kConsumerThreads) {
+                    const int j = i >> 3, r = i & 7;
+                    float out = 0.f;
+#pragma unroll 1
+                    for (int slot = 0; slot < p.K; ++slot) out = fmaf(S.route_w[slot], S.part[(j * p.K + slot) * 8 + r], out);
+                    const int n = (b + j * G) * 8 + r;
+                    if (i >= kConsumerThreads) resid = __ldcg(p.xa + n);
+                    p.xb[n] = __hadd(__float2half_rn(out), resid);
+                }
+            } else if (ph == 0) {
+                if (!last) {
+                    sq = warp_sum(sq);
+                    sk = warp_sum(sk);
+                    if (lane == 0) {
+                        S.red[warp] = sq;
+                        S.red[kWarps + warp] = sk;
+                    }
+                } else {
+#pragma unroll 1
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, pick_v, o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, pick_i, o);
+                        if (better(ov, oi, pick_v, pick_i)) {
+                            pick_v = ov;
+                            pick_i = oi;
+                        }
+                    }
+                    if (lane == 0) {
+                        S.red[warp] = pick_v;
+                        reinterpret_cast<int*>(S.red)[kWarps + warp] = pick_i;
+                    }
+                }
+            }
+            SUBSTAMP(4);
+        }
+        // ---- arrive at the grid barrier of this phase ------------------------------------------------------------
+        SUBSTAMP(5);
+        consumer_sync();
+        bar_target += gridDim.x;
+        if (tid == 0) {
+            if (ph == 0 && !last) {
+                // this block's share of the sums of squares of the q and k rows (its rows as stored, in fp16)
+                float a = 0.f, c = 0.f;
+                for (int w = 0; w < kStreamWarps; ++w) {
+                    a += S.red[w];
+                    c += S.red[kWarps + w];
+                }
+                p.stats[b] = a;
+                p.stats[G + b] = c;
+            } else if (ph == 0 && p.next_token != nullptr) {
+                // this block's candidate for the greedy pick
+                float best = S.red[0];
+                int bi = reinterpret_cast<int*>(S.red)[kWarps];
+                for (int w = 1; w < kStreamWarps; ++w) {
+                    const float v = S.red[w];
+                    const int i = reinterpret_cast<int*>(S.red)[kWarps + w];
+                    if (better(v, i, best, bi)) {
+                        best = v;
+                        bi = i;
+                    }
+                }
+                p.attn_part[2 * b] = best;
+                p.attn_part[2 * b + 1] = __int_as_float(bi);
+            }
+            // release at gpu scope is cumulative: it orders the writes of the whole block, which the block barrier
+            // above made visible to this thread, before the arrival
+            red_release_add(p.bar_counter, 1u);
+        }
+        SUBSTAMP(6);
+        if (++ph == 6) {
+            ph = 0;
+            ++l;
+            x_prev = p.xb;
+        }
+    }
+    if (p.next_token != nullptr && b == 0 && warp == 0) {
+        // greedy pick on the device: one candidate per block (written before the last barrier), merged here
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int bb = lane; bb < G; bb += 32) {
+            const float v = __ldcg(p.attn_part + 2 * bb);
+            const int i = __float_as_int(__ldcg(p.attn_part + 2 * bb + 1));
+            if (better(v, i, best, bi)) {
+                best = v;
+                bi = i;
+            }
+        }
+#pragma unroll 1
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ob, oi, best, bi)) {
+                best = ob;
+                bi = oi;
+            }
+        }
+        if (lane == 0) *p.next_token = (bi >= 0 && bi < p.V) ? bi : 0;
+    }
+    if (b == 0 && tid == 0) atomicAdd(p.bar_epoch, 1u);
+}
+
+}  // namespace tile
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+size_t tile_smem_bytes() { return sizeof(tile::Smem) + 128; }
+
+bool tile_eligible(const lemoq_step_desc& d) {
+    const int A = d.heads * d.head_dim;
+    if (d.group_size != 128) return false;
+    auto ok_dim = [](int n) { return n == 512 || n == 1024 || n == 2048; };  // row widths: powers of two, halves of whole 128-groups
+    if (!ok_dim(d.hidden) || !ok_dim(A) || !ok_dim(d.ffn)) return false;
+    if (d.head_dim != tile::kHeadDim || !d.kv_int8) return false;  // the fp16-KV arm runs as chained kernels
+    if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
+    if (d.top_k * d.ffn > 8192) return false;                      // planes of the routed experts' activations
+    if (d.vocab % 8 != 0 || d.layers + 1 > tile::kMaxLayers) return false;
+    return true;
+}
+
+// Attention splits per head for the tile form: every (head, split) unit should have at most one KV tile per
+// streaming warp.
+int tile_attention_splits(const lemoq_step_desc& d, int grid) {
+    const int tiles = (d.max_len + tile::kKvTile - 1) / tile::kKvTile;
+    int s = (tiles + tile::kStreamWarps - 1) / tile::kStreamWarps;
+    s = std::max(1, std::min(s, tile::kMaxSplits));
+    return std::max(1, std::min(s, grid / d.heads));
+}
+
+int tile_grid(const lemoq_step_desc& d) {
+    const bool verbose = getenv("LEMOQ_VERBOSE") != nullptr;
+    int dev = 0, sms = 0, per_sm = 0, coop = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(tile::step_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem_bytes()));
+    if (err == cudaSuccess)
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tile::step_tile_kernel, tile::kThreads, tile_smem_bytes());
+    if (verbose)
+        fprintf(stderr, "lemoq: tile step kernel: %s, sms %d, cooperative %d, blocks/SM %d, smem %zu\n", cudaGetErrorString(err), sms,
+                coop, per_sm, tile_smem_bytes());
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (!(coop && per_sm >= 1) || sms < d.heads) return 0;
+    // the partial sums of the down phase of the fullest block must fit their array
+    const int down_tiles = (d.hidden / 8 + sms - 1) / sms * d.top_k;
+    return down_tiles * 8 <= tile::kPartFloats ? sms : 0;
+}
+
+int launch_step_tile(const MegaParams& p, int grid, cudaStream_t stream) {
+    MegaParams local = p;
+    void* args[] = {&local};
+    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(tile::step_tile_kernel), dim3(grid), dim3(tile::kThreads),
+                                                        args, tile_smem_bytes(), stream);
+    if (err != cudaSuccess) return set_error(LEMOQ_ERR_CUDA, "cooperative launch of the step kernel failed: %s", cudaGetErrorString(err));
+    return LEMOQ_OK;
+}
+
+}  // namespace lemoq

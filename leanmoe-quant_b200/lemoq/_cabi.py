@@ -90,6 +90,7 @@ _SIGNATURES = {
     "lemoq_step_topk_ids": (c_void_p, [c_void_p]),
     "lemoq_step_router_logits": (c_void_p, [c_void_p]),
     "lemoq_step_phase_stamps": (c_void_p, [c_void_p]),
+    "lemoq_step_engine": (ctypes.c_char_p, [c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(sorted(_SIGNATURES))
