@@ -199,7 +199,7 @@ def run_reference(args) -> int:
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-# dram__bytes_read.sum + dram__bytes_write.sum of one step_mega_kernel launch, from one ncu capture of
+# dram__bytes_read.sum + dram__bytes_write.sum of one step_tile_kernel launch, from one ncu capture of
 # `python bench.py --steps 4 --warmup 3 --no-cpu-baseline` (summary under profiles/): (ctx, layers) -> bytes.
 WHOLE_STEP_DRAM_TRAFFIC = {(1024, 16): 1268504320 + 5156608}
 
@@ -378,8 +378,7 @@ def run_gpu(args) -> int:
             # duration is the device-timed step of the timed region above (CUDA events on the launching stream).
             achieved = budget["T"] / (dev_ms * 1e-3) / 1e9
             result["roofline"] = {
-                "bound": "hbm", "kernel": "%s (whole decode step: 16 x 6 phases + lm_head)"
-                                          % {"tile": "step_tile_kernel", "rows": "step_mega_kernel"}.get(session.capture_info.get("step_kernel"), "?"),
+                "bound": "hbm", "kernel": "step_tile_kernel (whole decode step: 16 x 6 phases + lm_head)",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "traffic": WHOLE_STEP_DRAM_TRAFFIC.get((ctx, model.config.num_hidden_layers)),
                 "bytes_per_launch": budget["T"], "us_per_launch": dev_ms * 1e3, "peak_source": peaks["source"],

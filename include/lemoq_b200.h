@@ -57,8 +57,7 @@ LEMOQ_API const char* lemoq_last_error(void);
  *   key 1  warps per block of the streaming kernels (1..16)
  *   key 4  step engine: 1 (default) the whole-step cooperative kernel when the shapes allow it,
  *          0 chained per-op kernels; takes effect at the next lemoq_step_create
- *   key 5  stages a warp of the whole-step kernel keeps in flight (1..8, capped by its ring)
- *   keys 2, 3, 6  timing experiments that skip copies or kernels: RESULTS ARE WRONG while set
+ * Every setting gives the same results up to fp32 summation order.
  * No counterpart in the reference, whose tile configs are module dicts
  * (ref: src/lemoq/kernels/moe_grouped.py:78, src/lemoq/kernels/_dequant_triton.py:83).
  */
@@ -323,9 +322,9 @@ LEMOQ_API int* lemoq_step_error_flag(lemoq_step* step);
  * checks): top_i (layers, top_k) int64 and router logits (layers, experts) fp16. */
 LEMOQ_API const int64_t* lemoq_step_topk_ids(lemoq_step* step);
 LEMOQ_API const void* lemoq_step_router_logits(lemoq_step* step);
-/* Name of the kernel form the plan runs as: "tile" (one cooperative kernel per step on 8-row tiles and the int8
- * tensor-core dot product), "rows" (one cooperative kernel per step on row pairs and the integer dot-product
- * instruction) or "chained" (6 kernels per layer).  Static string.  No counterpart in the reference. */
+/* Name of the form the plan runs as: "whole-step" (one cooperative kernel per step on 8-row weight tiles and the
+ * int8 tensor-core dot product) or "chained" (6 kernels per layer).  Static string.  No counterpart in the
+ * reference (ref for the step itself: benchmarks/cudagraph.py:713). */
 LEMOQ_API const char* lemoq_step_engine(lemoq_step* step);
 /* Device pointer to 6*layers + 2 global-timer stamps (ns) taken by the whole-step kernel at its start and
  * after each phase barrier of the last step; NULL when the step runs as chained kernels. */

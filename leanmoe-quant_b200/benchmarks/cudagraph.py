@@ -471,6 +471,19 @@ class StaticCacheDecodeSession:
         self.torch.cuda.synchronize()
         return self._step["workspace"][off: off + 8 * n].view(self.torch.int64).reshape(cfg.num_hidden_layers, -1).clone()
 
+    def step_router_logits(self) -> Any:
+        """``(layers, experts)`` fp16 router logits of the most recent step (step engine only)."""
+        if self._step is None:
+            raise RuntimeError("the step engine has not run")
+        from lemoq import _cabi
+
+        cfg = self.model.config
+        addr = _cabi.lib().lemoq_step_router_logits(self._step["handle"])
+        off = int(addr) - int(self._step["workspace"].data_ptr())
+        n = cfg.num_hidden_layers * cfg.num_experts
+        self.torch.cuda.synchronize()
+        return self._step["workspace"][off: off + 2 * n].view(self.torch.float16).reshape(cfg.num_hidden_layers, -1).clone()
+
     @property
     def step_next_token(self) -> Any:
         """Device scalar holding the token the native step engine picked in its last step (None for the per-op engine)."""

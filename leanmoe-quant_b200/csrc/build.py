@@ -15,14 +15,14 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ["cabi.cu", "gemv_w8.cu", "stream_gemv.cu", "moe_grouped.cu", "attn_decode.cu", "small_ops.cu", "step.cu", "step_mega.cu", "step_tile.cu", "batched_w8.cu"]
-HEADERS = ["common.cuh", "gemv_common.cuh", "stream.cuh", "stream_gemv.cuh", "step_mega.h", "kernels.h", os.path.join(ROOT, "include", "lemoq_b200.h")]
+SOURCES = ["cabi.cu", "gemv_w8.cu", "stream_gemv.cu", "moe_grouped.cu", "attn_decode.cu", "small_ops.cu", "step.cu", "step_tile.cu", "batched_w8.cu"]
+HEADERS = ["common.cuh", "gemv_common.cuh", "stream.cuh", "stream_gemv.cuh", "step_kernel.h", "kernels.h", os.path.join(ROOT, "include", "lemoq_b200.h")]
 LIB = os.path.join(HERE, "liblemoq_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
-] + os.environ.get("LEMOQ_NVCC_EXTRA", "").split()  # e.g. -DLEMOQ_MEGA_PROFILE for the cycle stamps of the whole-step kernel
+] + os.environ.get("LEMOQ_NVCC_EXTRA", "").split()
 
 
 def _newer(src: str, dst: str) -> bool:

@@ -31,6 +31,16 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// A token id read from device memory, clamped into [0, rows) (rows > 0); an id outside raises LEMOQ_FLAG_BAD_TOKEN.
+__device__ __forceinline__ int64_t checked_token(const int64_t* token, int64_t rows, int* err_flag) {
+    int64_t t = *token;
+    if (rows > 0 && (t < 0 || t >= rows)) {
+        if (err_flag && threadIdx.x == 0) atomicOr(err_flag, LEMOQ_FLAG_BAD_TOKEN);
+        t = t < 0 ? 0 : rows - 1;
+    }
+    return t;
+}
+
 // ---- loads -------------------------------------------------------------------
 // Streaming 128-bit load of read-once weight bytes: bypass L1 allocation.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -150,8 +160,9 @@ __device__ __forceinline__ float norm_elem(__half x, float rstd, __half w) {
 __device__ __forceinline__ int block_argmax_f16(const __half* __restrict__ v, int n, float* red_v, int* red_i) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    auto take = [&](float x, int i) {
-        if (x > best || (x == best && i < bi)) {
+    auto take = [&](float x, int i) {  // NaN counts as the largest value, the lowest index wins ties
+        const bool xn = x != x, bn = best != best;
+        if ((xn && (!bn || i < bi)) || (!xn && !bn && (x > best || (x == best && i < bi)))) {
             best = x;
             bi = i;
         }
@@ -178,7 +189,7 @@ __device__ __forceinline__ int block_argmax_f16(const __half* __restrict__ v, in
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < nwarp; ++w) take(red_v[w], red_i[w]);
-        return bi;
+        return (bi >= 0 && bi < n) ? bi : 0;
     }
     return -1;
 }

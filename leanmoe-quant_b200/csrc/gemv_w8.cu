@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(256) gemv_w8_kernel(GemvParams p) {
     pdl_trigger();
 
     int64_t x_off = static_cast<int64_t>(m) * p.x_stride;
-    if (p.x_token != nullptr) x_off = (*p.x_token) * static_cast<int64_t>(p.K);
+    if (p.x_token != nullptr) x_off = checked_token(p.x_token, p.token_rows, p.err_flag) * static_cast<int64_t>(p.K);
     float xr[NCH][16];
     if (NORM) {
         load_x_rmsnorm<NCH>(xr, p.x + x_off, p.norm_w, p.eps, p.K, lane, nullptr);
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) gemv_w8_kernel(GemvParams p) {
                 __half h = __float2half_rn(acc);
                 if (RESID) {
                     int64_t ro = static_cast<int64_t>(m) * p.resid_stride + n;
-                    if (p.resid_token != nullptr) ro = (*p.resid_token) * static_cast<int64_t>(p.N) + n;
+                    if (p.resid_token != nullptr) ro = checked_token(p.resid_token, p.token_rows, nullptr) * static_cast<int64_t>(p.N) + n;
                     h = __hadd(h, p.resid[ro]);
                 }
                 reinterpret_cast<__half*>(p.y)[yo] = h;

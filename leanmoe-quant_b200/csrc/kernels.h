@@ -44,6 +44,7 @@ struct GemvParams {
     const __half* x = nullptr;       // (M, K), row stride x_stride
     int64_t x_stride = 0;
     const int64_t* x_token = nullptr;  // optional: row = x + *x_token * K
+    int64_t token_rows = 0;          // rows behind x / resid when a token selects the row: ids outside [0, token_rows) are clamped and flagged
     const __half* norm_w = nullptr;  // (K) for the fused RMSNorm prologue
     float eps = 0.f;
     const int8_t* codes = nullptr;   // (N, K)
@@ -93,7 +94,6 @@ struct MoeParams {
     __half* out = nullptr;           // (T, H)
     const __half* resid = nullptr;   // optional (T, H): out = fp16(acc) + resid
     int* err_flag = nullptr;
-    int debug = 0;                   // timing experiments (lemoq_set_tuning key 2)
 };
 int launch_moe_gate_up(const MoeParams& p, bool w8, const LaunchCfg& lc);
 int launch_moe_down(const MoeParams& p, bool w8, const LaunchCfg& lc);

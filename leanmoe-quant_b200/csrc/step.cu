@@ -17,7 +17,7 @@
 #include <cstdio>
 #include <cstdlib>
 
-#include "step_mega.h"
+#include "step_kernel.h"
 
 struct lemoq_step {
     lemoq_step_desc d;
@@ -40,9 +40,8 @@ struct lemoq_step {
     // whole-step cooperative kernel
     unsigned int* bar_counter;
     unsigned int* bar_epoch;
-    lemoq::MegaLayer* mega_layers;  // device copy of the layer descriptors
-    int mega_grid;                  // 0 = chained kernels
-    int tile_kernel;                // the whole-step kernel is the tile form (step_tile.cu)
+    lemoq::StepLayer* whole_layers;  // device copy of the layer descriptors
+    int whole_grid;                  // blocks of the whole-step kernel; 0 = chained kernels
     float* stats;                   // per-block sums of squares of the q / k rows (tile form)
     unsigned long long* stamps;     // phase time stamps of the whole-step kernel
 };
@@ -98,8 +97,8 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(stats, float*, sizeof(float) * 2 * 1024);
     LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
-    LEMOQ_TAKE(mega_layers, lemoq::MegaLayer*, sizeof(lemoq::MegaLayer) * (d.layers + 1));
-    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2 + 256));
+    LEMOQ_TAKE(whole_layers, lemoq::StepLayer*, sizeof(lemoq::StepLayer) * (d.layers + 1));
+    LEMOQ_TAKE(stamps, unsigned long long*, sizeof(unsigned long long) * (6 * d.layers + 2));
 #undef LEMOQ_TAKE
     return c.off;
 }
@@ -135,10 +134,7 @@ __global__ void greedy_pick_kernel(const __half* logits, int n, int64_t* next_to
     if (threadIdx.x == 0) *next_token = tok;
 }
 
-int g_step_skip_mask = 0;  // timing experiments (lemoq_set_tuning key 3): bit i set = kernel class i is not launched (results wrong)
-int g_mega_debug = 0;      // lemoq_set_tuning key 6: timing experiments of the whole-step kernel (wrong results)
-int g_mega_depth = 8;      // lemoq_set_tuning key 5: stages a warp of the whole-step kernel keeps in flight (capped by its ring)
-int g_step_use_mega = 1;   // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
+int g_step_use_whole = 1;  // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
 }
 
 using namespace lemoq;
@@ -175,29 +171,23 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
     for (int l = 0; l < desc->layers; ++l) s->layers[l] = layers[l];
     s->splits = splits;
     carve(*desc, splits, s);
-    s->mega_grid = 0;
-    s->tile_kernel = 0;
-    const bool want_tile = g_step_use_mega == 1 && tile_eligible(*desc);
-    const bool want_mega = g_step_use_mega != 0 && mega_eligible(*desc);
-    if (getenv("LEMOQ_VERBOSE")) fprintf(stderr, "lemoq: whole-step kernel eligible: tile %d, row form %d\n", (int)want_tile, (int)want_mega);
-    if (want_tile || want_mega) {
-        int grid = want_tile ? tile_grid(*desc) : 0;
-        const bool use_tile = grid > 0 && grid <= 1024;
-        if (!use_tile) grid = want_mega ? mega_grid(*desc, splits) : 0;
+    s->whole_grid = 0;
+    const bool want_whole = g_step_use_whole != 0 && tile_eligible(*desc);
+    if (getenv("LEMOQ_VERBOSE")) fprintf(stderr, "lemoq: whole-step kernel eligible: %d\n", (int)want_whole);
+    if (want_whole) {
+        const int tgrid = tile_grid(*desc);
+        const int grid = tgrid <= 1024 ? tgrid : 0;
         if (grid > 0) {
             // attention units are (head, split) blocks: at most one per resident block
-            int ms = grid / desc->heads;
-            if (ms < 1) ms = 1;
-            if (ms > 9) ms = 9;  // the split merge of the whole-step kernel is unrolled for 9
-            if (use_tile) ms = tile_attention_splits(*desc, grid);
+            int ms = tile_attention_splits(*desc, grid);
             if (desc->attn_splits > 0 && desc->attn_splits < ms) ms = desc->attn_splits;
             // (the partials buffer doubles as the per-block candidate list of the greedy pick: 2 floats per block)
             if (desc->heads * ms <= grid && ms <= splits && desc->heads * splits * (desc->head_dim + 2) >= 2 * grid) {
-                MegaLayer* host = new (std::nothrow) MegaLayer[desc->layers + 1]();
+                StepLayer* host = new (std::nothrow) StepLayer[desc->layers + 1]();
                 if (host) {
                     for (int l = 0; l < desc->layers; ++l) {
                         const lemoq_layer_desc& L = layers[l];
-                        MegaLayer& m = host[l];
+                        StepLayer& m = host[l];
                         m.ln1 = reinterpret_cast<const __half*>(L.ln1);
                         m.ln2 = reinterpret_cast<const __half*>(L.ln2);
                         m.q_norm = reinterpret_cast<const __half*>(L.q_norm);
@@ -223,11 +213,10 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
                     host[desc->layers].qkv_codes = desc->lm_head_codes;
                     host[desc->layers].qkv_scale = reinterpret_cast<const __half*>(desc->lm_head_scale);
                     // set-up time only: the descriptors move to the device once (synchronous copy)
-                    const cudaError_t err = cudaMemcpy(s->mega_layers, host, sizeof(MegaLayer) * (desc->layers + 1), cudaMemcpyHostToDevice);
+                    const cudaError_t err = cudaMemcpy(s->whole_layers, host, sizeof(StepLayer) * (desc->layers + 1), cudaMemcpyHostToDevice);
                     delete[] host;
                     if (err == cudaSuccess) {
-                        s->mega_grid = grid;
-                        s->tile_kernel = use_tile ? 1 : 0;
+                        s->whole_grid = grid;
                         s->splits = ms;
                     }
                 }
@@ -248,10 +237,9 @@ extern "C" int* lemoq_step_error_flag(lemoq_step* s) { return s ? s->err_flag : 
 extern "C" const int64_t* lemoq_step_topk_ids(lemoq_step* s) { return s ? s->top_i : nullptr; }
 extern "C" const void* lemoq_step_router_logits(lemoq_step* s) { return s ? s->router_logits : nullptr; }
 extern "C" const char* lemoq_step_engine(lemoq_step* s) {
-    if (!s || s->mega_grid <= 0 || !g_step_use_mega) return "chained";
-    return s->tile_kernel ? "tile" : "rows";
+    return (s && s->whole_grid > 0) ? "whole-step" : "chained";
 }
-extern "C" const unsigned long long* lemoq_step_phase_stamps(lemoq_step* s) { return (s && s->mega_grid > 0) ? s->stamps : nullptr; }
+extern "C" const unsigned long long* lemoq_step_phase_stamps(lemoq_step* s) { return (s && s->whole_grid > 0) ? s->stamps : nullptr; }
 
 extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
     LEMOQ_REQUIRE(s, LEMOQ_ERR_INVALID, "step_run: null step");
@@ -264,8 +252,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
     lc.launch_count = &count;
     const float qk = (1.0f / sqrtf(static_cast<float>(d.head_dim))) * 1.4426950408889634f;
 
-    if (s->mega_grid > 0 && g_step_use_mega && g_step_skip_mask == 0) {
-        MegaParams p;
+    if (s->whole_grid > 0) {
+        StepParams p;
         p.layers = d.layers; p.H = d.hidden; p.heads = d.heads; p.D = d.head_dim; p.E = d.experts; p.K = d.top_k;
         p.F = d.ffn; p.V = d.vocab; p.group = d.group_size; p.S = d.max_len; p.splits = s->splits;
         p.kv_int8 = d.kv_int8; p.norm_topk = d.norm_topk_prob; p.eps = d.eps; p.qk_scale_log2 = qk;
@@ -278,19 +266,14 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.token = d.token; p.cache_position = d.cache_position; p.filled = d.filled_len;
         p.logits = reinterpret_cast<__half*>(d.logits);
         p.next_token = d.next_token;
-        p.L = s->mega_layers;
+        p.L = s->whole_layers;
         p.err_flag = s->err_flag; p.bar_counter = s->bar_counter; p.bar_epoch = s->bar_epoch;
-        p.attn_counters = s->attn_counters;
-        p.qkv = s->qkv; p.attn = s->attn; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
+        p.qkv = s->qkv; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
         p.router_logits = s->router_logits; p.top_w = s->top_w; p.top_i = s->top_i; p.attn_part = s->attn_part;
         p.stats = s->stats;
         p.barriers_per_launch = 6 * d.layers + 1;
         p.stamps = s->stamps;
-        p.depth = g_mega_depth;
-        p.debug = g_mega_debug;
-        if (int rc = s->tile_kernel ? launch_step_tile(p, s->mega_grid, static_cast<cudaStream_t>(stream))
-                                    : launch_step_mega(p, s->mega_grid, static_cast<cudaStream_t>(stream)))
-            return rc;
+        if (int rc = launch_step_tile(p, s->whole_grid, static_cast<cudaStream_t>(stream))) return rc;
         if (launches) *launches = 1;
         return LEMOQ_OK;
     }
@@ -304,6 +287,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             GemvParams p;
             p.x = x_prev;
             p.x_token = x_token;
+            p.token_rows = d.vocab;
             p.norm_w = reinterpret_cast<const __half*>(L.ln1);
             p.eps = d.eps;
             p.codes = L.qkv_codes;
@@ -313,8 +297,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.group_size = d.group_size;
             p.y = s->qkv;
             p.err_flag = s->err_flag;
-            if (!(g_step_skip_mask & 1))
-                if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
+            if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
         }
         // K2: attention with fused q/k norm, RoPE, KV write
         {
@@ -348,8 +331,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.part = s->attn_part;
             p.counters = s->attn_counters;
             p.err_flag = s->err_flag;
-            if (!(g_step_skip_mask & 2))
-                if (int rc = launch_attn_decode(p, d.kv_int8 != 0, true, lc)) return rc;
+            if (int rc = launch_attn_decode(p, d.kv_int8 != 0, true, lc)) return rc;
         }
         // K3: x1 = x_prev + W8(o) . attn
         {
@@ -364,8 +346,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.err_flag = s->err_flag;
             p.resid = x_prev;
             p.resid_token = x_token;
-            if (!(g_step_skip_mask & 4))
-                if (int rc = launch_gemv_w8(p, 1, false, true, false, lc)) return rc;
+            p.token_rows = d.vocab;
+            if (int rc = launch_gemv_w8(p, 1, false, true, false, lc)) return rc;
         }
         // K4: h2 = RMSNorm(x1); router logits, softmax, top-k
         {
@@ -383,8 +365,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.top_w = s->top_w;
             p.top_i = s->top_i + static_cast<int64_t>(l) * d.top_k;
             p.counter = s->route_counter;
-            if (!(g_step_skip_mask & 8))
-                if (int rc = launch_route(p, true, lc)) return rc;
+            if (int rc = launch_route(p, true, lc)) return rc;
         }
         // K5 + K6: grouped experts, x2 = x1 + moe
         {
@@ -406,10 +387,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
             p.out = s->xb;
             p.resid = s->xa;
             p.err_flag = s->err_flag;
-            if (!(g_step_skip_mask & 16))
-                if (int rc = launch_moe_gate_up(p, true, lc)) return rc;
-            if (!(g_step_skip_mask & 32))
-                if (int rc = launch_moe_down(p, true, lc)) return rc;
+            if (int rc = launch_moe_gate_up(p, true, lc)) return rc;
+            if (int rc = launch_moe_down(p, true, lc)) return rc;
         }
         x_prev = s->xb;
         x_token = nullptr;
@@ -419,6 +398,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         GemvParams p;
         p.x = x_prev;
         p.x_token = x_token;
+        p.token_rows = d.vocab;
         p.norm_w = reinterpret_cast<const __half*>(d.final_norm);
         p.eps = d.eps;
         p.codes = d.lm_head_codes;
@@ -428,8 +408,7 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.group_size = d.group_size;
         p.y = d.logits;
         p.err_flag = s->err_flag;
-        if (!(g_step_skip_mask & 64))
-            if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
+        if (int rc = launch_gemv_w8(p, 1, true, false, false, lc)) return rc;
     }
     if (d.next_token != nullptr) {
         LaunchCfg plain = lc;

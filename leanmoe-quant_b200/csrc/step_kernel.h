@@ -1,11 +1,11 @@
-// Parameter block of the whole-step cooperative kernel (step_mega.cu), shared with the step engine.
+// Parameter block of the whole-step cooperative kernel (step_tile.cu), shared with the step engine.
 #pragma once
 
 #include "kernels.h"
 
 namespace lemoq {
 
-struct MegaLayer {
+struct StepLayer {
     const __half *ln1, *ln2, *q_norm, *k_norm;
     const int8_t* qkv_codes;
     const __half* qkv_scale;
@@ -23,7 +23,7 @@ struct MegaLayer {
     __half* vs;
 };
 
-struct MegaParams {
+struct StepParams {
     int layers, H, heads, D, E, K, F, V, group, S, splits, kv_int8, norm_topk;
     float eps, qk_scale_log2;
     const __half *embed, *final_norm, *lm_scale, *rope_cos, *rope_sin;
@@ -32,29 +32,21 @@ struct MegaParams {
     const int32_t* filled;
     __half* logits;
     int64_t* next_token;  // optional: argmax(logits)
-    const MegaLayer* L;  // device array
+    const StepLayer* L;   // device array: the layers, then a pseudo layer whose q.k.v rows are the lm_head
     int* err_flag;
-    unsigned int *bar_counter, *bar_epoch, *attn_counters;
-    __half *qkv, *attn, *xa, *xb, *act, *router_logits, *top_w;
+    unsigned int *bar_counter, *bar_epoch;
+    __half *qkv, *xa, *xb, *act, *router_logits, *top_w;
     int64_t* top_i;
-    float* attn_part;
-    float* stats;                // tile kernel: per-block sums of squares of the q rows, then of the k rows (2 x grid floats)
+    float* attn_part;            // (m, l, acc[D]) partial of every (head, split) unit; at the end the per-block greedy candidates
+    float* stats;                // per-block sums of squares of the q rows, then of the k rows (2 x grid floats)
     int barriers_per_launch;
-    int debug;                   // timing experiments (wrong results)
-    int depth;                   // stages a warp keeps in flight (clamped to the ring size)
     unsigned long long* stamps;  // optional: 6*layers + 2 phase time stamps of the last step
 };
 
-size_t mega_smem_bytes();
-bool mega_eligible(const lemoq_step_desc& d);
-int mega_grid(const lemoq_step_desc& d, int splits);  // blocks to launch (one per SM), 0 = unavailable
-int launch_step_mega(const MegaParams& p, int grid, cudaStream_t stream);
-
-// the same step on 16-row tiles and the int8 tensor-core dot product (step_tile.cu)
 size_t tile_smem_bytes();
 bool tile_eligible(const lemoq_step_desc& d);
 int tile_grid(const lemoq_step_desc& d);  // blocks to launch (one per SM), 0 = unavailable
 int tile_attention_splits(const lemoq_step_desc& d, int grid);
-int launch_step_tile(const MegaParams& p, int grid, cudaStream_t stream);
+int launch_step_tile(const StepParams& p, int grid, cudaStream_t stream);
 
 }  // namespace lemoq

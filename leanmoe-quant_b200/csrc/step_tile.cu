@@ -41,7 +41,7 @@
 #include <cstdio>
 #include <cstdlib>
 
-#include "step_mega.h"
+#include "step_kernel.h"
 #include "stream.cuh"
 
 namespace lemoq {
@@ -96,21 +96,7 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-#ifdef LEMOQ_TILE_PROFILE
-// development build only: global-timer stamps inside the phases of layer 1 (block 0, thread 0)
-#define SUBSTAMP(idx)                                                                 \
-    do {                                                                              \
-        if (p.stamps != nullptr && l == 1 && blockIdx.x == 0 && threadIdx.x == 0) {   \
-            p.stamps[6 * p.layers + 2 + ph * 8 + (idx)] = clock64();                  \
-        }                                                                             \
-    } while (0)
-#else
-#define SUBSTAMP(idx) \
-    do {              \
-    } while (0)
-#endif
-
-__device__ __forceinline__ void stamp(const MegaParams& p, int slot) {
+__device__ __forceinline__ void stamp(const StepParams& p, int slot) {
     if (p.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -330,7 +316,7 @@ struct Smem {
     int route_id[32];
     float route_w[32];
     Geo geo;
-    MegaLayer layers[kMaxLayers];
+    StepLayer layers[kMaxLayers];
 };
 
 __device__ __forceinline__ int udiv_small(int q, int magic) { return (q * magic) >> 16; }  // q / d for q < 65536 / d, magic = ceil(65536 / d)
@@ -343,7 +329,7 @@ __device__ __forceinline__ int udiv_small(int q, int magic) { return (q * magic)
 // the top_k routed experts as consecutive tiles).
 __device__ __noinline__ void issue_tile(const Smem& S, int layer, int kind, int lt, uint32_t stage, uint32_t bar) {
     const Geo& geo = S.geo;
-    const MegaLayer& L = S.layers[layer];
+    const StepLayer& L = S.layers[layer];
     const int lane = threadIdx.x & 31;
     const char* src = nullptr;
     uint32_t bytes = 0, dst = 0, tx = 0;
@@ -625,7 +611,7 @@ __device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, 
 // The attention output as the o_proj input: a half warp merges the splits of one head (partials (m, l, acc[128]) of
 // the (head, split) units, taken four splits at a time in split order), rounds to fp16 and builds the planes of the
 // head's group.  Lane i of the half warp holds dimensions 8i .. 8i+7.
-__device__ __noinline__ void prepare_attention_output(const MegaParams& p, Smem& S) {
+__device__ __noinline__ void prepare_attention_output(const StepParams& p, Smem& S) {
     constexpr int D = kHeadDim;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, lane16 = lane & 15;
     const int head = warp * 2 + (lane >> 4);
@@ -687,7 +673,7 @@ __device__ __noinline__ void prepare_attention_output(const MegaParams& p, Smem&
 // Warp 0: q (RMSNorm over all heads, RoPE, softmax scale, digit planes).  Warp 1 / warp 2 of the block that owns
 // the new position: the new K row (norm, RoPE) / V row into the fp16 cache and, quantised, into the int8 mirror
 // and shared memory.  Lane i holds dimensions 4i .. 4i+3; the RoPE partner (d +- 64) lives 16 lanes away.
-__device__ __noinline__ void attention_prologue(const MegaParams& p, const MegaLayer& L, Smem& S) {
+__device__ __noinline__ void attention_prologue(const StepParams& p, const StepLayer& L, Smem& S) {
     constexpr int D = kHeadDim;
     AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
     const Geo& geo = S.geo;
@@ -860,7 +846,7 @@ __device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, co
 }
 
 // Merge of the block's warps into the unit's partial (m, l, acc[128]).
-__device__ __noinline__ void attention_partial(const MegaParams& p, Smem& S) {
+__device__ __noinline__ void attention_partial(const StepParams& p, Smem& S) {
     constexpr int D = kHeadDim;
     AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
     const Geo& geo = S.geo;
@@ -903,7 +889,7 @@ __device__ __noinline__ bool better(float v, int i, float best, int bi) {
     return v > best || (v == best && i < bi);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_constant__ MegaParams p) {
+__global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -913,7 +899,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
     {
         const uint64_t* src = reinterpret_cast<const uint64_t*>(p.L);
         uint64_t* dst = reinterpret_cast<uint64_t*>(S.layers);
-        const int words = (p.layers + 1) * static_cast<int>(sizeof(MegaLayer) / 8);
+        const int words = (p.layers + 1) * static_cast<int>(sizeof(StepLayer) / 8);
         for (int i = tid; i < words; i += kThreads) dst[i] = src[i];
     }
 
@@ -1020,19 +1006,17 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
             stamp(p, step);
         }
         if (step == nphases) break;
-        const MegaLayer& L = S.layers[l];
+        const StepLayer& L = S.layers[l];
         const bool last = l == p.layers;
         const int ntiles = last ? geo.nt[6] : geo.nt[ph];
         const int lt0 = warp - cbase + (warp < cbase ? kStreamWarps : 0);  // this warp's first tile of the phase
         cbase = (cbase + ntiles) % kStreamWarps;
         float sq = 0.f, sk = 0.f;  // phase A: sums of squares of the q / k values this lane stored
-        SUBSTAMP(0);
 
         if (ph == 1) {
             if (geo.has_unit) {
                 AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
                 attention_prologue(p, L, S);
-                SUBSTAMP(1);
                 {
                     float m_i = -INFINITY, l_i = 0.f;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1060,10 +1044,8 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         sm.wl[warp] = l_i;
                     }
                 }
-                SUBSTAMP(3);
                 consumer_sync();
                 attention_partial(p, S);
-                SUBSTAMP(4);
             }
         } else {
             // ---- block-wide preparation of the phase -----------------------------------------------------
@@ -1084,7 +1066,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     if (lane == 0) S.ready_layer = l;  // the producers may start the expert tiles of this layer
                 }
                 consumer_sync();
-                SUBSTAMP(2);
             } else if (ph == 2) {
                 prepare_attention_output(p, S);
             } else {
@@ -1092,7 +1073,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 prepare(p.eps, ph == 0 ? x_prev : (ph == 3 ? p.xa : p.act), ph == 0 ? L.ln1 : (ph == 3 ? L.ln2 : nullptr), K,
                         ph == 5 ? (p.K * p.F) >> 7 : K >> 7, ph == 5 ? S.big : S.xplanes, ph == 5 ? fsx : S.xsx, ph == 3 ? S.xh : nullptr, S.red);
             }
-            SUBSTAMP(1);
             // the residual of this thread's down row (in flight while the tiles are worked on)
             __half resid_f = __float2half_rn(0.f);
             if (ph == 5 && tid < geo.f_blocks * 8) resid_f = __ldcg(p.xa + (b + (tid >> 3) * G) * 8 + (tid & 7));
@@ -1107,9 +1087,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
                     c_par ^= 1u;
                     float val;
-#ifdef LEMOQ_TILE_PROFILE
-                    const long long tc0 = clock64();
-#endif
                     if (ph == 3) {
                         val = tile_f16(my_stage, p.H, g, t, S.xh);
                         val += __shfl_xor_sync(0xffffffffu, val, 1);
@@ -1136,12 +1113,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         val += __shfl_xor_sync(0xffffffffu, val, 1);
                         val += __shfl_xor_sync(0xffffffffu, val, 2);
                     }
-#ifdef LEMOQ_TILE_PROFILE
-                    if (l == 1 && lane == 0 && p.stamps && val != 1234.5f) {
-                        // per (phase, block < 16): cycles of one tile's arithmetic
-                        if (b < 16) p.stamps[6 * p.layers + 2 + 48 + ph * 16 + b] = static_cast<unsigned long long>(clock64() - tc0);
-                    }
-#endif
                     stage_release(empty_bar);
                     if (ph == 0) {
                         const int n = tg * 8 + g;
@@ -1172,7 +1143,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     }
                 }
             }
-            SUBSTAMP(3);
             if (ph == 5) {
                 // the routed experts of a down row are consecutive tiles: routing-weighted sum in slot order
                 const int nrows = geo.f_blocks * 8;
@@ -1212,10 +1182,8 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     }
                 }
             }
-            SUBSTAMP(4);
         }
         // ---- arrive at the grid barrier of this phase ------------------------------------------------------------
-        SUBSTAMP(5);
         consumer_sync();
         bar_target += gridDim.x;
         if (tid == 0) {
@@ -1247,7 +1215,6 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
             // above made visible to this thread, before the arrival
             red_release_add(p.bar_counter, 1u);
         }
-        SUBSTAMP(6);
         if (++ph == 6) {
             ph = 0;
             ++l;
@@ -1331,8 +1298,8 @@ int tile_grid(const lemoq_step_desc& d) {
     return down_tiles * 8 <= tile::kPartFloats ? sms : 0;
 }
 
-int launch_step_tile(const MegaParams& p, int grid, cudaStream_t stream) {
-    MegaParams local = p;
+int launch_step_tile(const StepParams& p, int grid, cudaStream_t stream) {
+    StepParams local = p;
     void* args[] = {&local};
     const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(tile::step_tile_kernel), dim3(grid), dim3(tile::kThreads),
                                                         args, tile_smem_bytes(), stream);

@@ -20,11 +20,7 @@ constexpr int kDownStages = 4;
 // Tunables (set through lemoq_set_tuning; defaults are the measured best).
 int g_stream_warps = 16;
 int g_dot_mode = DOT_F16_FOLD;
-extern int g_step_skip_mask;
-extern int g_step_use_mega;
-extern int g_mega_depth;
-extern int g_mega_debug;
-int g_debug_skip_scale_copy = 0;  // timing experiments only: results are wrong when set
+extern int g_step_use_whole;
 
 // ---------------------------------------------------------------------------
 // Dense GEMV: a task is ROWS=2 consecutive weight rows (codes and scales contiguous).
@@ -65,7 +61,7 @@ __global__ void __launch_bounds__(kMaxStreamWarps * 32, 1) stream_gemv_w8_kernel
     pdl_trigger();
 
     int64_t x_off = 0;
-    if (p.x_token != nullptr) x_off = (*p.x_token) * static_cast<int64_t>(p.K);
+    if (p.x_token != nullptr) x_off = checked_token(p.x_token, p.token_rows, p.err_flag) * static_cast<int64_t>(p.K);
     XSlice<NCH, MODE> xs;
     load_xslice<NCH, MODE, NORM>(xs, p.x + x_off, p.norm_w, p.eps, p.K, lane);
 
@@ -92,7 +88,7 @@ __global__ void __launch_bounds__(kMaxStreamWarps * 32, 1) stream_gemv_w8_kernel
             __half h = __float2half_rn(lane == 0 ? acc0 : acc1);
             if (RESID) {
                 int64_t ro = n;
-                if (p.resid_token != nullptr) ro = (*p.resid_token) * static_cast<int64_t>(p.N) + n;
+                if (p.resid_token != nullptr) ro = checked_token(p.resid_token, p.token_rows, nullptr) * static_cast<int64_t>(p.N) + n;
                 h = __hadd(h, p.resid[ro]);
             }
             reinterpret_cast<__half*>(p.y)[n] = h;
@@ -134,19 +130,13 @@ __global__ void __launch_bounds__(kMaxStreamWarps * 32, 1) stream_gate_up_kernel
             e = e < 0 ? 0 : p.E - 1;
         }
         const int64_t rg = e * 2 * p.F + n, ru = rg + p.F;
-        if (p.debug & 1) {
-            mbar_expect_tx(ring.bar(s), code_bytes);
-            bulk_g2s(ring.stage(s), codes + rg * p.H, row_bytes, ring.bar(s));
-            bulk_g2s(ring.stage(s) + row_bytes, codes + ru * p.H, row_bytes, ring.bar(s));
-            return;
-        }
         mbar_expect_tx(ring.bar(s), code_bytes + 2 * srow_bytes);
         bulk_g2s(ring.stage(s), codes + rg * p.H, row_bytes, ring.bar(s));
         bulk_g2s(ring.stage(s) + row_bytes, codes + ru * p.H, row_bytes, ring.bar(s));
         bulk_g2s(ring.stage(s) + code_bytes, p.gu_scale + rg * groups, srow_bytes, ring.bar(s));
         bulk_g2s(ring.stage(s) + code_bytes + srow_bytes, p.gu_scale + ru * groups, srow_bytes, ring.bar(s));
     };
-    if (lane == 0 && !(p.debug & 4)) {
+    if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kStreamStages; ++s) {
             const int t = first + s * stride;
@@ -160,19 +150,16 @@ __global__ void __launch_bounds__(kMaxStreamWarps * 32, 1) stream_gate_up_kernel
     int it = 0;
     for (int task = first; task < n_tasks; task += stride, ++it) {
         const int s = it % kStreamStages;
-        if (!(p.debug & 4) && !mbar_wait(ring.bar(s), (it / kStreamStages) & 1)) {
+        if (!mbar_wait(ring.bar(s), (it / kStreamStages) & 1)) {
             flag_timeout(p.err_flag);
             return;
         }
         const unsigned char* st = my + static_cast<size_t>(s) * stage_bytes;
         const __half* sc = reinterpret_cast<const __half*>(st + code_bytes);
-        float g = 0.f, u = 0.f;
-        if (!(p.debug & 2)) {
-            g = row_partial<NCH, MODE>(st, sc, lm, xs);
-            u = row_partial<NCH, MODE>(st + row_bytes, sc + groups, lm, xs);
-        }
+        float g = row_partial<NCH, MODE>(st, sc, lm, xs);
+        float u = row_partial<NCH, MODE>(st + row_bytes, sc + groups, lm, xs);
         __syncwarp();
-        if (lane == 0 && !(p.debug & 4)) {
+        if (lane == 0) {
             const int nt = task + kStreamStages * stride;
             if (nt < n_tasks) issue(s, nt);
         }
@@ -363,24 +350,8 @@ int set_stream_tuning(int key, int value) {
         g_stream_warps = value;
         return LEMOQ_OK;
     }
-    if (key == 2) {
-        g_debug_skip_scale_copy = value;
-        return LEMOQ_OK;
-    }
-    if (key == 3) {
-        g_step_skip_mask = value;
-        return LEMOQ_OK;
-    }
-    if (key == 4) {
-        g_step_use_mega = value;
-        return LEMOQ_OK;
-    }
-    if (key == 6) {
-        g_mega_debug = value;
-        return LEMOQ_OK;
-    }
-    if (key == 5 && value >= 1 && value <= 8) {
-        g_mega_depth = value;
+    if (key == 4 && (value == 0 || value == 1)) {
+        g_step_use_whole = value;
         return LEMOQ_OK;
     }
     return set_error(LEMOQ_ERR_INVALID, "set_tuning: unknown key %d or value %d out of range", key, value);
@@ -449,9 +420,7 @@ static int launch_stream_gate_up_mode(const MoeParams& p, const LaunchCfg& lc) {
     dim3 grid(grid_for(p.K * p.F, warps)), block(warps * 32);
     auto kern = stream_gate_up_kernel<NCH, MODE>;
     if (int rc = set_smem(kern, smem)) return rc;
-    MoeParams q = p;
-    q.debug = g_debug_skip_scale_copy;
-    return launch_kernel(kern, grid, block, smem, lc, q);
+    return launch_kernel(kern, grid, block, smem, lc, p);
 }
 
 template <int NCH>
