@@ -8,20 +8,25 @@ lm_head W8 + per-token INT8 KV, all-ones prompt of ``ctx`` tokens prefilled, the
 A "step" is one decoded token = one replay of the captured step graph.
 
 Printed JSON line (rank 0):
-  value   tokens/s with the step inputs already on the device: K graph replays at advancing
-          positions, device-timed with CUDA events, no host read-back inside the region.
-  e2e     tokens/s through the public session API with host buffers: per step the token id and
-          position are copied from pinned host memory, the graph runs, the next token id is read
-          back (this is the reference's replay_timed_step loop).
+  value   tokens/s with everything on the device: the step feeds itself (its pick, the next slot and the next
+          length go into its own input scalars), the timed region is K graph replays, device-timed with CUDA events.
+  e2e     tokens/s through the public session API with host buffers: ``replay_chained(32)`` copies the first
+          step's inputs from pinned host memory (32 B), replays 32 steps and reads the 32 token ids back (8 B each)
+          with one synchronisation; ``e2e.per_token_sync`` is the reference's loop (inputs in, replay, synchronise,
+          token out, every step).
   roofline  the dominant kernel.  With the whole-step kernel (default) that is the one launch per step:
           the step's algorithmic bytes / the device-timed step against the measured HBM copy bandwidth.
           With chained kernels it is the expert gate/up GEMV timed alone on L2-flushed launches (also
           reported beside the whole-step figure).
-  cpu_baseline  the CPU oracle (a port of the reference's torch CPU path) on a bounded sample.
+  cpu_baseline  the CPU oracle (a port of the reference's torch CPU path) on a bounded sample (one GPU only).
+  ctx4096 / config4 / expert_parallel  sub-records: benchmark configuration 3 (ctx 4096, int8 and fp16 KV),
+          configuration 4 (isolated L2-flushed kernels) and configuration 5 (64 sequences x ctx 2048, experts
+          sharded over the N ranks with NCCL all-to-all; at N = 1 the same decoder without the exchange).
 
 ``--impl reference`` times only that CPU implementation (all host threads) on the same configuration.
 With ``--gpus N`` (under torchrun) batch-1 decode does not shard: every rank runs an independent
-replica ("replicas only"), the reported value is the sum over ranks with the max-over-ranks time.
+replica ("replicas only"), the reported value is the sum over ranks with the max-over-ranks time; the
+``expert_parallel`` sub-record is the one measurement in which the N ranks work on one job.
 """
 
 from __future__ import annotations
@@ -54,6 +59,15 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, earlier measurement on this pool)"}
 
 
+def workload_config(ctx: int, layers: int, world: int, bytes_per_step: int) -> dict:
+    """The ``config`` block both arms print: the workload, nothing about how an arm runs it."""
+    return {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, "
+                        "ctx %d, one decoded token per step (benchmark configuration 2)" % ctx,
+            "ctx": ctx, "layers": layers,
+            "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (bytes_per_step / 1e9),
+            "parallelism": "replicas only" if world > 1 else "single GPU"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -70,7 +84,7 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -183,13 +197,19 @@ def run_reference(args) -> int:
     ms = 1000.0 * sum(times) / len(times)
     value = 1000.0 / ms
     sample = "%d decode steps of the 16-layer canonical model at ctx %d (synthetic int8 codes, random fp16 KV)" % (steps, args.ctx)
+    from benchmarks.bytes import CANONICAL_QUANT, ModelSpec, byte_budget
+    from lemoq.model import OlmoeConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    budget = byte_budget(ModelSpec.from_config(OlmoeConfig()), args.ctx + max(3, args.warmup) + steps // 2 + 1, CANONICAL_QUANT, kv_int8=True)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, ctx %d" % args.ctx,
-                   "ctx": args.ctx, "layers": spec.layers},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(args.ctx, spec.layers, world, budget["T"]),
+        "run": {"weights": "synthetic int8 codes and fp16 scales of the canonical shapes (the work of a step does not depend on the values)",
+                "threads": torch.get_num_threads()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -249,6 +269,99 @@ def time_dominant_kernel(model, peaks, iters: int = 20) -> dict:
             "peak_source": peaks["source"], "timing": "CUDA events, isolated launches, 256 MB L2 flush before each"}
 
 
+def sub_ctx4096(model, peaks, device: str, steps: int = 64) -> dict:
+    """Benchmark configuration 3: the same model at ctx 4096, attending to the int8 mirror (whole-step kernel) and,
+    for comparison, to the fp16 cache (kv_int8 switched off: chained kernels).  Device-timed self-feeding replays."""
+    import torch
+
+    from benchmarks.bytes import CANONICAL_QUANT, ModelSpec, byte_budget
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+
+    ctx, horizon = 4096, steps + 8
+    spec = ModelSpec.from_config(model.config)
+    prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
+    out = {"ctx": ctx, "steps": steps, "what": "benchmark configuration 3; device-timed, %d self-feeding graph replays after 5 warm-up steps" % steps}
+    for name, kv_int8 in (("kv_int8", True), ("kv_fp16", False)):
+        old = os.environ.get("LEMOQ_KV_INT8")
+        os.environ["LEMOQ_KV_INT8"] = "1" if kv_int8 else "0"
+        try:
+            session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="step")
+            session.capture(warmup=3)
+        finally:
+            if old is None:
+                os.environ.pop("LEMOQ_KV_INT8", None)
+            else:
+                os.environ["LEMOQ_KV_INT8"] = old
+        session.reset()
+        for _ in range(5):
+            session.replay(synchronize=True)
+        session._set_step_inputs(skip_mask=session._replay_skip_mask())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(session.stream):
+            e0.record(session.stream)
+            for _ in range(steps):
+                session.graph.replay()
+            e1.record(session.stream)
+        session.stream.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        budget = byte_budget(spec, ctx + 5 + steps // 2 + 1, CANONICAL_QUANT, kv_int8=kv_int8)
+        floor = budget["T"] / (peaks["hbm_gbs"] * 1e9) * 1e3
+        out[name] = {"ms_per_token": ms, "tok_per_s": 1000.0 / ms, "bytes_per_step": budget["T"], "byte_floor_ms": floor,
+                     "floor_fraction": floor / ms, "kernels_per_step": session.capture_info.get("kernels_per_step"),
+                     "step_kernel": session.capture_info.get("step_kernel"), "error_flags": session.step_error_flags()}
+        session.close()
+        del session
+        torch.cuda.empty_cache()
+    return out
+
+
+def sub_config4(peaks) -> dict:
+    """Benchmark configuration 4 and the per-kernel rows: the isolated, L2-flushed microbenchmarks of
+    benchmarks/bench_kernels.py (grouped MoE at 1/4/16 tokens with int8 and fp16 weights, dense W8 GEMV at the
+    q.k.v / o_proj / lm_head shapes, attention at ctx 1024 / 4096)."""
+    import contextlib
+    import io
+
+    from benchmarks import bench_kernels as bk
+
+    buf = io.StringIO()
+    timer = bk.Timer(10)
+    with contextlib.redirect_stdout(buf):
+        bk.bench_moe(timer, [1, 4, 16], peaks["hbm_gbs"])
+        bk.bench_dense(timer, peaks["hbm_gbs"])
+        bk.bench_attn(timer, peaks["hbm_gbs"])
+    rows = []
+    for line in buf.getvalue().splitlines():
+        line = line.strip()
+        if line.startswith("{"):
+            r = json.loads(line)
+            rows.append({k: r[k] for k in ("subject", "bytes", "us_cold", "gbs", "frac_of_peak", "frac_minus_floor") if k in r}
+                        | {k: r[k] for k in ("tokens", "weights", "ctx", "kv") if k in r})
+    return {"what": "isolated launches, 256 MB L2 flush before each, median of 10, GB/s = analytic bytes / time; "
+                    "frac_minus_floor subtracts the empty event-pair time (%.1f us)" % timer.floor_us,
+            "peak_gbs": peaks["hbm_gbs"], "rows": rows}
+
+
+EP_GOLDEN = os.path.join(ROOT, "tests", "golden", "expert_parallel_tokens.json")
+
+
+def sub_expert_parallel(model, device: str, world: int, rank: int) -> dict:
+    """Benchmark configuration 5 on this run's GPUs: 64 sequences x ctx 2048 in lockstep, experts sharded over the
+    ranks, static-capacity NCCL all-to-all, the whole step in one CUDA graph.  ``tokens_match_one_gpu`` compares the
+    digest of all decoded tokens with the committed digest of the same run on one GPU."""
+    from benchmarks import expert_parallel as ep
+
+    rec = ep.measure(model, device=device, world=world, rank=rank, sequences=64, ctx=2048, steps=32, warmup=3,
+                     exchange="static", graph=True, split=True)
+    rec.pop("tokens")
+    want = None
+    if os.path.exists(EP_GOLDEN):
+        with open(EP_GOLDEN) as fh:
+            want = json.load(fh).get("sha256")
+    rec["tokens_match_one_gpu"] = (rec["token_digest"] == want) if want else None
+    return rec
+
+
 def run_gpu(args) -> int:
     import torch
 
@@ -302,25 +415,51 @@ def run_gpu(args) -> int:
     barrier()
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # the step scalars of all K steps are on the device before the clock starts; each step moves its 32 bytes into
-    # the step's input buffer with one device copy and replays the graph
-    step_inputs = torch.tensor([[int(session.current_token_id), start_pos + i, start_pos + i, start_pos + i + 1] for i in range(steps)],
-                               dtype=torch.int64, device=device)
+    # the step feeds itself on the device (its pick, the next slot and the next length go into its own input scalars):
+    # the scalars of the first step are set before the clock starts, the timed region is K graph replays
+    native = session.capture_info.get("engine") == "step"
+    if native:
+        session._set_step_inputs(skip_mask=session._replay_skip_mask())
     torch.cuda.synchronize()
     with torch.cuda.stream(session.stream):
         ev0.record(session.stream)
         for i in range(steps):
-            if session.capture_info.get("engine") == "step":
-                session.buffers.packed.copy_(step_inputs[i])
+            if native:
                 session.graph.replay()
-            else:  # the per-op engine also keeps an attention mask up to date
+            else:  # the per-op engine needs its inputs and an attention mask from the host every step
                 session.position = start_pos + i
                 session.replay(synchronize=False)
         ev1.record(session.stream)
     session.stream.synchronize()
     barrier()
     dev_ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
-    # ---------------- e2e: host buffers in, token id out, every step ----------------
+    # ---------------- e2e: the public session API with host buffers ----------------
+    # replay_chained(B): the first step's inputs come from pinned host memory (one 32-byte copy), B replays run with
+    # no host work in between, the B token ids come back in one copy to pinned host memory; the host continues from
+    # the last token.  B = 32 is the reference's decode horizon (32 greedy steps).
+    block = 32
+    session.reset()
+    for _ in range(warmup):
+        session.replay(synchronize=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record(session.stream)
+    done = 0
+    if native:
+        while done < steps:
+            n = min(block, steps - done)
+            session.replay_chained(n)
+            done += n
+    else:
+        for i in range(steps):
+            session.replay(synchronize=True)
+    e1.record(session.stream)
+    session.stream.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1000.0 / steps
+    barrier()
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / steps, wall_ms))
+    # the reference's loop for comparison: inputs in, replay, synchronize, token out, every single step
     session.reset()
     for _ in range(warmup):
         session.replay(synchronize=True)
@@ -328,28 +467,23 @@ def run_gpu(args) -> int:
     pinned_out = torch.zeros(1, dtype=torch.int64).pin_memory()
     b = session.buffers
     tok, pos = session.current_token_id, session.position
+    nsync = min(steps, 100)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     with torch.cuda.stream(session.stream):
-        e0.record(session.stream)
-        for i in range(steps):
-            # H2D of this step's inputs: one 32-byte copy lands in all four step scalars (views of one buffer)
+        for i in range(nsync):
             b.pack_step(pinned_in, token=tok, position=pos + i)
             b.packed.copy_(pinned_in, non_blocking=True)
             session.graph.replay()
-            picked = session.step_next_token  # the native step picks the token itself; the per-op engine leaves logits
+            picked = session.step_next_token
             if picked is None:
                 picked = session.logits.reshape(-1).argmax().reshape(1)
-            pinned_out.copy_(picked, non_blocking=True)  # D2H of the result
+            pinned_out.copy_(picked, non_blocking=True)
             session.stream.synchronize()
             tok = int(pinned_out[0])
-        e1.record(session.stream)
-    session.stream.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1000.0 / steps
+    per_token_sync_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0 / nsync)
     barrier()
     clocks = sampler.stop()
-    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / steps, wall_ms))
 
     spec = ModelSpec.from_config(model.config)
     budget = byte_budget(spec, ctx + warmup + steps // 2 + 1, CANONICAL_QUANT, kv_int8=True)
@@ -358,17 +492,20 @@ def run_gpu(args) -> int:
         "metric": METRIC, "value": world * 1000.0 / dev_ms, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, "
-                               "ctx %d, one CUDA graph per step (benchmark configuration 2)" % ctx,
-                   "ctx": ctx, "layers": model.config.num_hidden_layers, "engine": session.capture_info.get("engine"),
-                   "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0",
-                   "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (budget["T"] / 1e9),
-                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "config": workload_config(ctx, model.config.num_hidden_layers, world, budget["T"]),
+        "run": {"engine": session.capture_info.get("engine"), "step_kernel": session.capture_info.get("step_kernel"),
+                "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0, RTN-quantised on the GPU",
+                "execution": "one CUDA graph per step"},
         "ms_per_token": dev_ms, "bytes_per_step": budget["T"], "byte_floor_ms": floor_ms,
         "floor_fraction": floor_ms / dev_ms, "floor_fraction_e2e": floor_ms / e2e_ms,
-        "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": 32,
-                "d2h_bytes_per_step": 8},
-        "gpu_launches": launches_per_step * steps * 2, "kernels_per_step": launches_per_step,
+        "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 32.0 / block if native else 32, "d2h_bytes_per_step": 8,
+                "api": "StaticCacheDecodeSession.replay_chained(32): 32 B of step inputs in per 32 tokens, 8 B per token out, "
+                       "one synchronisation per 32 tokens" if native else "StaticCacheDecodeSession.replay per token",
+                "per_token_sync": {"value": world * 1000.0 / per_token_sync_ms, "unit": UNIT, "ms_per_step": per_token_sync_ms,
+                                   "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 8,
+                                   "what": "the reference's loop: inputs in, replay, synchronise, token out, every step"}},
+        "gpu_launches": launches_per_step * (2 * steps + nsync), "kernels_per_step": launches_per_step,
         "step_kernel": session.capture_info.get("step_kernel"), "clocks": clocks,
     }
     if rank == 0:
@@ -387,14 +524,28 @@ def run_gpu(args) -> int:
         else:
             result["roofline"] = isolated
         result["roofline"]["step_floor_fraction"] = floor_ms / dev_ms
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             result["cpu_baseline"] = cpu_baseline_from_session(session, model, spec, ctx, warmup)
     session.close()
+    del session
+    torch.cuda.empty_cache()
+    full_size = args.layers is None
+    if not args.no_sub_records and full_size:
+        if rank == 0 and ctx != 4096:
+            result["ctx4096"] = sub_ctx4096(model, peaks, device)
+        if rank == 0:
+            result["config4"] = sub_config4(peaks)
+        barrier()
+        ep_rec = sub_expert_parallel(model, device, world, rank)  # every rank takes part
+        if rank == 0:
+            result["expert_parallel"] = ep_rec
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
+        from benchmarks.expert_parallel import shutdown_process_group
+
         dist.barrier()
-        dist.destroy_process_group()
+        shutdown_process_group()
     return 0
 
 
@@ -415,7 +566,7 @@ def cpu_baseline_from_session(session, model, spec_bytes, ctx: int, warmup: int)
     n = 6
     times = time_oracle_steps(wq, st, session.seed_token_id, ctx, n, 1)
     ms = 1000.0 * sum(times) / len(times)
-    return {"value": 1000.0 / ms, "unit": UNIT, "ms_per_step": ms, "cores": cores, "kind": "port",
+    return {"value": 1000.0 / ms, "unit": UNIT, "ms_per_step": ms, "cores": torch.get_num_threads(), "kind": "port",
             "sample": "%d greedy decode steps of the same model and prefilled cache on the CPU oracle (1 warm-up)" % n}
 
 
@@ -427,8 +578,9 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--engine", default="auto", choices=["auto", "step", "ops"])
-    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--layers", type=int, default=None, help="decode a model of this many layers instead of 16 (no sub-records)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub-records", action="store_true", help="skip the ctx 4096, isolated-kernel and expert-parallel sub-records")
     ap.add_argument("--step-kernel", default="default", choices=["default", "chained", "whole"],
                     help="step engine: chained kernels with PDL, or the single cooperative whole-step kernel")
     args = ap.parse_args()

@@ -305,6 +305,15 @@ typedef struct lemoq_step_desc {
     int64_t* next_token;    /* optional device scalar: the step also writes argmax(logits) here (the
                                first maximal index, as the reference's greedy loop picks it:
                                ref benchmarks/cudagraph.py:756-762); NULL = not wanted          */
+    int self_feed;          /* 1 (needs next_token): at its very end the step also stores the picked token
+                               into *token and adds 1 to *cache_position and *filled_len, so that K
+                               launches in a row decode K tokens greedily with no host work in between
+                               (the reference's loop syncs and reads the token back per step:
+                               ref benchmarks/cudagraph.py:756-762).  A host that sets the three
+                               scalars before every launch, as the reference does, is not affected. */
+    int64_t* token_log;     /* optional device array of max_len entries (needs next_token): the step also
+                               stores its pick at token_log[*cache_position], so a host that launched K
+                               steps in a row reads the K tokens back with one copy; NULL = not wanted */
 } lemoq_step_desc;
 
 typedef struct lemoq_step lemoq_step; /* host-side plan, owns no device memory */

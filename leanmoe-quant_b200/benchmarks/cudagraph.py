@@ -249,6 +249,7 @@ class StaticCacheDecodeSession:
         self._use_pdl = (os.environ.get("LEMOQ_PDL", "1") == "1") if use_pdl is None else bool(use_pdl)
         self._attn_splits = int(attn_splits)
         self._step = None  # native step plan (built lazily, after the first prefill)
+        self._chain_host = None  # pinned read-back buffer of replay_chained
         self.engine = None
         self.after_prefill = None  # optional callable(session): runs at the end of every prefill
         self.prefill()
@@ -398,12 +399,15 @@ class StaticCacheDecodeSession:
         desc.logits = _cabi.ptr(logits)
         next_token = torch.zeros(1, dtype=torch.int64, device=self.device)  # the step's own greedy pick
         desc.next_token = _cabi.ptr(next_token)
+        desc.self_feed = 1  # the step leaves its pick, the next slot and the next length in the input scalars
+        token_log = torch.zeros(max_len, dtype=torch.int64, device=self.device)  # token_log[position] = the step's pick
+        desc.token_log = _cabi.ptr(token_log)
         nbytes = int(_cabi.lib().lemoq_step_workspace_bytes(ctypes.byref(desc)))
         workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         desc.workspace, desc.workspace_bytes = _cabi.ptr(workspace), nbytes
         handle = ctypes.c_void_p()
         _cabi.check(_cabi.lib().lemoq_step_create(ctypes.byref(desc), layers, ctypes.byref(handle)), "lemoq_step_create")
-        self._step = {"handle": handle, "logits": logits, "next_token": next_token, "workspace": workspace, "keep": keep, "kv_int8": kv_int8,
+        self._step = {"handle": handle, "logits": logits, "next_token": next_token, "token_log": token_log, "workspace": workspace, "keep": keep, "kv_int8": kv_int8,
                       "desc": desc, "layers": layers}
         self.capture_info["pdl"] = bool(self._use_pdl)
 
@@ -616,6 +620,40 @@ class StaticCacheDecodeSession:
         except Exception as exc:  # noqa: BLE001
             raise CudaGraphCaptureError("replay", exc) from exc
 
+    def replay_chained(self, steps: int) -> list[int]:
+        """``steps`` greedy decode steps with no host work in between (native step engine only): the step inputs go to
+        the device once, every replay leaves its pick, the next slot and the next length in the input scalars for the
+        next one and logs its token; one read-back of ``steps`` token ids at the end.  Replaces ``steps`` rounds of the
+        reference's set-inputs / replay / synchronize / read-back loop (benchmarks/cudagraph.py:756-762)."""
+        if self.graph is None or self._step is None or self.capture_info.get("engine") != "step":
+            raise RuntimeError("replay_chained needs the captured native step engine")
+        if steps <= 0:
+            raise ValueError("steps must be positive")
+        if self.position + steps > self.config.max_cache_len:
+            raise RuntimeError("replay_chained: exceeded StaticCache capacity (%d + %d > %d)"
+                               % (self.position, steps, self.config.max_cache_len))
+        torch = self.torch
+        if self._chain_host is None or self._chain_host.numel() < steps + 4:
+            self._chain_host = torch.zeros(max(steps, 64) + 4, dtype=torch.int64).pin_memory()
+        if self.current_token_id is None:
+            raise RuntimeError("prefill must run before decode")
+        try:
+            with torch.cuda.stream(self.stream), torch.no_grad():
+                # the step scalars of the first step: one 32-byte copy from pinned host memory into the packed buffer
+                host_in = self.buffers.pack_step(self._chain_host[-4:], token=self.current_token_id, position=self.position)
+                self.buffers.packed.copy_(host_in, non_blocking=True)
+                for _ in range(steps):
+                    self.graph.replay()
+                log = self._step["token_log"][self.position: self.position + steps]
+                self._chain_host[:steps].copy_(log, non_blocking=True)
+            self.stream.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            raise CudaGraphCaptureError("replay", exc) from exc
+        tokens = [int(v) for v in self._chain_host[:steps].tolist()]
+        self.position += steps
+        self.current_token_id = tokens[-1]
+        return tokens
+
     def set_position(self, position: int) -> None:
         if position < 0 or position >= self.config.max_cache_len:
             raise RuntimeError("position %d 超出 StaticCache 容量 %d" % (position, self.config.max_cache_len))
@@ -631,8 +669,12 @@ class StaticCacheDecodeSession:
         torch = self.torch
         if self.graph is None:
             raise RuntimeError("capture must succeed before timing")
+        saved = self.position
+        if self._step is not None:  # the native step advances its own position: stay inside the cache
+            self.position = max(0, min(self.position, self.config.max_cache_len - iters - 4))
         with torch.cuda.stream(self.stream):
             self._set_step_inputs(skip_mask=self._replay_skip_mask())
+            self.position = saved
             for _ in range(3):
                 self.graph.replay()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

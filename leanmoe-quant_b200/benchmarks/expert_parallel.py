@@ -6,9 +6,10 @@ Per layer and rank:  route the local tokens -> **all-to-all dispatch** of the (t
 ranks that own their experts (fp16 activation row + global expert id, pairs sorted by expert so that a
 rank streams each resident expert's weights once) -> grouped expert GEMV on the received pairs ->
 **all-to-all combine** of the fp16 expert outputs -> routing-weighted sum at the home rank in slot order
-(fp32, one rounding) + residual.  32 all-to-alls per step over NCCL (NVLink/NVSwitch); pair counts are
-exchanged first and read on the host, so this form is not graph-capturable (a static-capacity variant
-would be).  Buffers are received into local memory before any kernel touches them; no peer pointers.
+(fp32, one rounding) + residual.  Two all-to-alls per layer over NCCL (NVLink/NVSwitch), 32 per step.  Two forms of
+the exchange: **static** (default) sends every peer a fixed number of pair slots, reads nothing on the host and is
+captured, all-to-alls included, in one CUDA graph; **dynamic** exchanges the pair counts first and reads them on the
+host.  Buffers are received into local memory before any kernel touches them; no peer pointers.
 
 There is no counterpart in the reference (its runner is batch 1, `benchmarks/runner.py`); the oracle for
 this mode is the same decoder at world size 1: results must match it token for token, which the
@@ -84,7 +85,7 @@ def all_to_all_rows(rows: Any, send_counts: list, recv_counts: list, *, world: i
 
 
 def expert_parallel_moe(h: Any, top_w: Any, top_i: Any, *, experts: int, world: int, rank: int,
-                        expert_fn: Callable[[Any, Any], Any], group: Any = None) -> Any:
+                        expert_fn: Callable[[Any, Any], Any], group: Any = None, section: Any = None) -> Any:
     """``h (T, H)`` fp16 normalised activations, ``top_w/top_i (T, K)``.  ``expert_fn(x (R, H), local_ids (R,))
     -> (R, H)`` fp16 runs this rank's experts on the received pairs.  Returns the fp32-combined, fp16-rounded
     MoE output ``(T, H)`` of the local tokens."""
@@ -110,49 +111,77 @@ def expert_parallel_moe(h: Any, top_w: Any, top_i: Any, *, experts: int, world: 
     return out.to(h.dtype)
 
 
+class _NoSection:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _no_section(name: str) -> Any:
+    return _NoSection()
+
+
+ID_COLS = 8  # fp16 columns appended to a dispatched row (the first holds the expert id; 8 keep rows 16-byte aligned)
+
+
 def expert_parallel_moe_static(h: Any, top_w: Any, top_i: Any, *, experts: int, world: int, rank: int,
-                               expert_fn: Callable[[Any, Any], Any], group: Any = None) -> Any:
+                               expert_fn: Callable[[Any, Any], Any], group: Any = None, section: Any = _no_section) -> Any:
     """The same exchange with a STATIC capacity: every rank sends every peer a buffer of T*K pair slots (the
     worst case), unused slots carry the expert id ``experts`` and are sorted behind the real pairs, where
-    ``expert_fn`` must ignore them.  No tensor shape and no collective size depends on the routing and nothing
-    is read on the host, so the whole step can be captured in a CUDA graph.  Same results as
-    :func:`expert_parallel_moe` bit for bit: every real pair meets the same kernel with the same inputs."""
+    ``expert_fn`` must ignore them.  The expert id rides in the row itself (one extra fp16 column group: ids up to
+    2048 are exact in fp16), so a layer needs two all-to-alls: rows out, rows back.  No tensor shape and no
+    collective size depends on the routing and nothing is read on the host, so the whole step can be captured in a
+    CUDA graph.  Same results as :func:`expert_parallel_moe` bit for bit: every real pair meets the same kernel with
+    the same inputs.  ``section(name)`` returns a context manager (timing hooks of the benchmark)."""
     import torch.distributed as dist
 
+    if experts > 2048:
+        raise ValueError("experts=%d: the id column of the static exchange is fp16 (exact up to 2048)" % experts)
     t, k = int(top_i.shape[0]), int(top_i.shape[1])
     pairs_n, hidden, epr, dev = t * k, int(h.shape[1]), experts // world, h.device
-    flat = top_i.reshape(-1)
-    order = torch.argsort(flat, stable=True)
-    sorted_e = flat[order]
-    dest = torch.div(sorted_e, epr, rounding_mode="floor")
-    counts = (dest.reshape(-1, 1) == torch.arange(world, device=dev).reshape(1, -1)).sum(dim=0)
-    starts = torch.cumsum(counts, dim=0) - counts
-    pos = torch.arange(pairs_n, device=dev) - starts[dest]
-    send_x = h.new_zeros((world, pairs_n, hidden))
-    send_e = torch.full((world, pairs_n), experts, dtype=torch.int64, device=dev)
-    send_x[dest, pos] = h[torch.div(order, k, rounding_mode="floor")]
-    send_e[dest, pos] = sorted_e
+    with section("dispatch-combine glue"):
+        flat = top_i.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        sorted_e = flat[order]
+        dest = torch.div(sorted_e, epr, rounding_mode="floor")
+        counts = (dest.reshape(-1, 1) == torch.arange(world, device=dev).reshape(1, -1)).sum(dim=0)
+        starts = torch.cumsum(counts, dim=0) - counts
+        pos = torch.arange(pairs_n, device=dev) - starts[dest]
+        send = h.new_zeros((world, pairs_n, hidden + ID_COLS))
+        send[:, :, hidden] = float(experts)
+        send[dest, pos, :hidden] = h[torch.div(order, k, rounding_mode="floor")]
+        send[dest, pos, hidden] = sorted_e.to(h.dtype)
     if world > 1:
-        recv_x, recv_e = torch.empty_like(send_x), torch.empty_like(send_e)
-        dist.all_to_all_single(recv_x, send_x, group=group)
-        dist.all_to_all_single(recv_e, send_e, group=group)
+        with section("all-to-all"):
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=group)
     else:
-        recv_x, recv_e = send_x, send_e
-    local = torch.where(recv_e == experts, torch.full_like(recv_e, epr), recv_e - rank * epr).reshape(-1)
-    perm = torch.argsort(local, stable=True)
-    y_sorted = expert_fn(recv_x.reshape(-1, hidden)[perm].contiguous(), local[perm].contiguous())
-    y = torch.empty_like(y_sorted)
-    y[perm] = y_sorted
-    y = y.reshape(world, pairs_n, hidden)
+        recv = send
+    with section("dispatch-combine glue"):
+        recv_e = recv[:, :, hidden].reshape(-1).to(torch.int64)
+        local = torch.where(recv_e == experts, torch.full_like(recv_e, epr), recv_e - rank * epr)
+        perm = torch.argsort(local, stable=True)
+        x_sorted = recv.reshape(-1, hidden + ID_COLS)[perm, :hidden].contiguous()
+        ids_sorted = local[perm].contiguous()
+    with section("expert kernels"):
+        y_sorted = expert_fn(x_sorted, ids_sorted)
+    with section("dispatch-combine glue"):
+        y = torch.empty_like(y_sorted)
+        y[perm] = y_sorted
+        y = y.reshape(world, pairs_n, hidden)
     if world > 1:
-        back = torch.empty_like(y)
-        dist.all_to_all_single(back, y, group=group)
+        with section("all-to-all"):
+            back = torch.empty_like(y)
+            dist.all_to_all_single(back, y, group=group)
     else:
         back = y
-    pairs = torch.empty((pairs_n, hidden), dtype=h.dtype, device=dev)
-    pairs[order] = back[dest, pos]
-    out = (pairs.reshape(t, k, -1).float() * top_w.reshape(t, k, 1).float()).sum(dim=1)
-    return out.to(h.dtype)
+    with section("dispatch-combine glue"):
+        pairs = torch.empty((pairs_n, hidden), dtype=h.dtype, device=dev)
+        pairs[order] = back[dest, pos]
+        out = (pairs.reshape(t, k, -1).float() * top_w.reshape(t, k, 1).float()).sum(dim=1)
+        return out.to(h.dtype)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -243,6 +272,54 @@ class ExpertParallelDecoder:
         self.pos_t = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.filled_t = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sections = None  # name -> list of (start, end) CUDA events while a timing split is being taken
+
+    def _section(self, name: str) -> Any:
+        if self.sections is None:
+            return _NoSection()
+        dec = self
+
+        class _Timed:
+            def __enter__(self_inner):
+                self_inner.start = torch.cuda.Event(enable_timing=True)
+                self_inner.start.record()
+                return self_inner
+
+            def __exit__(self_inner, *exc):
+                end = torch.cuda.Event(enable_timing=True)
+                end.record()
+                dec.sections.setdefault(name, []).append((self_inner.start, end))
+                return False
+
+        return _Timed()
+
+    def timing_split(self, tokens: Any, steps: int = 3) -> dict:
+        """Microseconds per step by category, from CUDA events around the sections of ``steps`` EAGER steps at the
+        current position (the position does not advance; a captured graph cannot be split this way, so launch gaps of
+        the eager glue are inside the figures)."""
+        graph, self.graph = self.graph, None
+        pos = self.position
+        try:
+            self._forward_at(tokens)  # warm
+            self.sections = {}
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(steps):
+                self._forward_at(tokens)
+            t1.record()
+            torch.cuda.synchronize(self.device)
+            out = {name: sum(a.elapsed_time(b) for a, b in evs) * 1e3 / steps for name, evs in self.sections.items()}
+            out["whole eager step"] = t0.elapsed_time(t1) * 1e3 / steps
+        finally:
+            self.sections = None
+            self.graph = graph
+            self.position = pos
+        return {k: round(v, 1) for k, v in out.items()}
+
+    def _forward_at(self, tokens: Any) -> Any:
+        self.pos_t.fill_(self.position)
+        self.filled_t.fill_(self.position + 1)
+        return self._forward(tokens)
 
     # -- one lockstep step: tokens (b,) int64 -> logits (b, V) fp16 -------------------------------------
     def step(self, tokens: Any) -> Any:
@@ -303,10 +380,13 @@ class ExpertParallelDecoder:
         moe_fn = expert_parallel_moe_static if self.static_exchange else expert_parallel_moe
         x = self.model.model.embed_tokens.weight[tokens]  # (b, H) fp16
         eps = float(cfg.rms_norm_eps)
+        sec = self._section
         for i, layer in enumerate(self.model.model.layers):
             attn, mlp = layer.self_attn, layer.mlp
             pk = attn._lemoq_packed_qkv
             gs = int(pk.group_size)
+            dense = sec("dense + attention")
+            dense.__enter__()
             h1 = rms_norm_fused(x, layer.input_layernorm.weight, eps)
             qkv = linear(h1, pk.packed, pk.scale, gs)  # (b, 3A)
             q = rms_norm_fused(qkv[:, :a].contiguous(), attn.q_norm.weight, eps)
@@ -329,45 +409,46 @@ class ExpertParallelDecoder:
             h2 = rms_norm_fused(x1, layer.post_attention_layernorm.weight, eps)
             logits = torch.matmul(h2, mlp._static_router.t())  # (b, E) fp16: a plain library GEMM
             top_w, top_i = routing_softmax_topk(logits, top_k=cfg.num_experts_per_tok, norm_topk_prob=bool(cfg.norm_topk_prob))
+            dense.__exit__(None, None, None)
             moe = moe_fn(h2, top_w.to(torch.float16), top_i, experts=cfg.num_experts, world=self.world,
-                         rank=self.rank, expert_fn=self.local[i], group=self.group)
+                         rank=self.rank, expert_fn=self.local[i], group=self.group, section=sec)
             x = moe + x1
-        hn = rms_norm_fused(x, self.model.model.norm.weight, eps)
-        lm = self.model.lm_head
-        return linear(hn, lm.packed, lm.scale, int(lm.group_size))
+        with sec("dense + attention"):
+            hn = rms_norm_fused(x, self.model.model.norm.weight, eps)
+            lm = self.model.lm_head
+            return linear(hn, lm.packed, lm.scale, int(lm.group_size))
 
     def error_flags(self) -> int:
         return int(self.err.item())
 
 
-def run(args: Any) -> int:
+def token_digest(hist: Any) -> str:
+    """Digest of a (sequences, steps) int64 token table (little-endian bytes, SHA-256)."""
+    import hashlib
+
+    return hashlib.sha256(hist.to(torch.int64).cpu().contiguous().numpy().tobytes()).hexdigest()
+
+
+def measure(model: Any, *, device: str, world: int, rank: int, sequences: int = 64, ctx: int = 2048, steps: int = 32,
+            warmup: int = 3, exchange: str = "static", graph: bool = True, identical: bool = False, split: bool = True) -> dict:
+    """Prefill the shared prompt, build this rank's share of the lockstep decoder, decode ``warmup + steps`` tokens
+    per sequence and time the last ``steps`` (device events, max over ranks).  ``model`` is the canonical quantised
+    module tree.  Returns the result record (every rank; token table and digest are those of all sequences)."""
+    import gc
+
     import torch.distributed as dist
 
     from benchmarks.cudagraph import StaticCacheDecodeSession
-    from benchmarks.runner import build_model, install_replacements
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    device = "cuda:%d" % local_rank
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    steps, ctx, seqs = args.steps, args.ctx, args.sequences
-    horizon = steps + args.warmup + 2
-    model = build_model(seed=0, device=device, layers=args.layers)
-    install_replacements(model, attn="kernel", moe="grouped", quant_cfg={"bit_width": "w8a16", "dequant": "fused", "group_size": 128},
-                         rmsnorm="fused", ctx=ctx, max_new_tokens=horizon, device=device)
+    horizon = steps + warmup + 2
     prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
-    session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="ops")
-    dec = ExpertParallelDecoder(model, session, sequences=seqs, world=world, rank=rank, static_exchange=args.exchange == "static")
-    if args.graph:
+    session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="ops")  # prefills
+    dec = ExpertParallelDecoder(model, session, sequences=sequences, world=world, rank=rank, static_exchange=exchange == "static")
+    if graph:
         dec.capture()
-        if os.environ.get("LEMOQ_VERBOSE"):
-            print("rank %d: step graph captured" % rank, file=sys.stderr, flush=True)
-    # the literal configuration decodes 64 identical sequences; distinct first tokens make the exchange non-trivial
+    # the literal configuration decodes identical sequences; distinct first tokens make the exchange non-trivial
     first = torch.arange(dec.first_seq, dec.first_seq + dec.b, device=device, dtype=torch.int64)
-    tokens = (first * 7 + 2) % model.config.vocab_size if not args.identical else torch.full_like(first, int(session.seed_token_id))
+    tokens = (first * 7 + 2) % model.config.vocab_size if not identical else torch.full_like(first, int(session.seed_token_id))
     history = []
 
     def barrier():
@@ -376,12 +457,9 @@ def run(args: Any) -> int:
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         tokens = dec.step(tokens).float().argmax(dim=-1)
         history.append(tokens.clone())
-    if os.environ.get("LEMOQ_VERBOSE"):
-        torch.cuda.synchronize()
-        print("rank %d: warm-up steps done" % rank, file=sys.stderr, flush=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
@@ -401,34 +479,78 @@ def run(args: Any) -> int:
         gathered = [torch.empty_like(hist) for _ in range(world)]
         dist.all_gather(gathered, hist)
         hist = torch.cat(gathered, dim=0)
+    parts = dec.timing_split(tokens) if split else None
     flags = dec.error_flags()
+    # a captured graph holds collective kernels of the process group: destroy it (not only drop the name) before
+    # anybody tears the communicator down, whose shutdown waits for every captured plan to be released
+    if dec.graph is not None:
+        dec.graph.reset()
+        dec.graph = None
+    session.close()
+    del dec, session
+    gc.collect()
+    torch.cuda.synchronize()
+    ms_step = float(ms.item()) / steps
+    cfg = model.config
+    return {"metric": "decode_tokens_per_s_batched_expert_parallel", "value": sequences * 1000.0 / ms_step, "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "data": "synthetic",
+            "config": {"workload": "%d sequences x ctx %d lockstep greedy decode, W8A16 + INT8 KV, experts sharded %d per GPU, "
+                                   "NCCL all-to-all dispatch/combine (benchmark configuration 5)" % (sequences, ctx, cfg.num_experts // world),
+                       "layers": cfg.num_hidden_layers, "identical_sequences": bool(identical), "exchange": exchange,
+                       "cuda_graph": bool(graph), "all_to_alls_per_step": 2 * cfg.num_hidden_layers if world > 1 else 0},
+            "eager_split_us_per_step": parts, "error_flags": flags, "token_digest": token_digest(hist), "tokens": hist.cpu()}
+
+
+def shutdown_process_group(limit_s: float = 60.0) -> None:
+    """``destroy_process_group`` with a host-side time limit.  The communicator's shutdown waits until every CUDA graph
+    that captured one of its collectives has been destroyed; :func:`measure` destroys its graph first.  Should the
+    shutdown still not return within ``limit_s`` the process leaves without it (all results are out by then)."""
+    import threading
+
+    import torch.distributed as dist
+
+    def give_up():
+        sys.stderr.write("expert_parallel: process-group shutdown did not return within %.0f s; leaving without it\n" % limit_s)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+    timer = threading.Timer(limit_s, give_up)
+    timer.daemon = True
+    timer.start()
+    dist.destroy_process_group()
+    timer.cancel()
+
+
+def run(args: Any) -> int:
+    import torch.distributed as dist
+
+    from benchmarks.runner import build_model, install_replacements
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = "cuda:%d" % local_rank
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    model = build_model(seed=0, device=device, layers=args.layers)
+    install_replacements(model, attn="kernel", moe="grouped", quant_cfg={"bit_width": "w8a16", "dequant": "fused", "group_size": 128},
+                         rmsnorm="fused", ctx=args.ctx, max_new_tokens=args.steps + args.warmup + 2, device=device)
+    result = measure(model, device=device, world=world, rank=rank, sequences=args.sequences, ctx=args.ctx, steps=args.steps,
+                     warmup=args.warmup, exchange=args.exchange, graph=args.graph, identical=args.identical)
+    hist = result.pop("tokens")
     if rank == 0:
-        ms_step = float(ms.item()) / steps
-        result = {"metric": "decode_tokens_per_s_batched_expert_parallel", "value": seqs * 1000.0 / ms_step, "unit": "tok/s",
-                  "n_gpus": world, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-                  "scaling": "strong", "data": "synthetic",
-                  "config": {"workload": "%d sequences x ctx %d lockstep greedy decode, W8A16 + INT8 KV, experts sharded %d per GPU, "
-                                         "NCCL all-to-all dispatch/combine (benchmark configuration 5)" % (seqs, ctx, model.config.num_experts // world),
-                             "layers": model.config.num_hidden_layers, "identical_sequences": bool(args.identical),
-                             "exchange": args.exchange, "cuda_graph": bool(args.graph)},
-                  "error_flags": flags}
         if args.check_against:
             ref = torch.load(args.check_against)
-            result["tokens_match_reference_run"] = bool(tuple(ref.shape) == tuple(hist.shape) and torch.equal(ref, hist.cpu()))
+            result["tokens_match_reference_run"] = bool(tuple(ref.shape) == tuple(hist.shape) and torch.equal(ref, hist))
         print(json.dumps(result))
         if args.tokens_out:
-            torch.save(hist.cpu(), args.tokens_out)
+            torch.save(hist, args.tokens_out)
     if world > 1:
         dist.barrier()
-        if args.graph:
-            # Tearing the communicator down while a captured graph still references its kernels blocked here
-            # (seen on B200 / NCCL 2.28): drop the graph, finish all work, and leave without the collective teardown.
-            dec.graph = None
-            torch.cuda.synchronize()
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
-        dist.destroy_process_group()
+        shutdown_process_group()
     return 0
 
 
@@ -438,7 +560,7 @@ def main() -> int:
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
+    ap.add_argument("--layers", type=int, default=None, help="decode a model of this many layers instead of 16")
     ap.add_argument("--exchange", default="static", choices=["static", "dynamic"],
                     help="static: fixed-capacity all-to-all, nothing read on the host; dynamic: counts exchanged and read per layer")
     ap.add_argument("--graph", action="store_true", help="capture the step (with its all-to-alls) in one CUDA graph; static exchange only")

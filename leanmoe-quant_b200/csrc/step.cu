@@ -120,6 +120,7 @@ static int validate(const lemoq_step_desc& d) {
     LEMOQ_REQUIRE(d.embed && d.final_norm && d.lm_head_codes && d.lm_head_scale && d.rope_cos && d.rope_sin &&
                       d.token && d.cache_position && d.filled_len && d.logits && d.workspace,
                   LEMOQ_ERR_INVALID, "step: null pointer in descriptor");
+    LEMOQ_REQUIRE(!d.self_feed || d.next_token, LEMOQ_ERR_INVALID, "step: self_feed needs next_token");
     return LEMOQ_OK;
 }
 
@@ -127,11 +128,21 @@ static int validate(const lemoq_step_desc& d) {
 
 namespace lemoq {
 // argmax(logits) -> *next_token, first maximal index (one block)
-__global__ void greedy_pick_kernel(const __half* logits, int n, int64_t* next_token) {
+__global__ void greedy_pick_kernel(const __half* logits, int n, int64_t* next_token, int64_t* token, int64_t* cache_position,
+                                   int32_t* filled, int64_t* token_log, int max_len) {
     __shared__ float rv[32];
     __shared__ int ri[32];
     const int tok = block_argmax_f16(logits, n, rv, ri);
-    if (threadIdx.x == 0) *next_token = tok;
+    if (threadIdx.x == 0) {
+        *next_token = tok;
+        const int64_t pos = *cache_position;
+        if (token_log != nullptr && pos >= 0 && pos < max_len) token_log[pos] = tok;
+        if (token != nullptr) {  // self-feeding step: the pick is the next step's input
+            *token = tok;
+            *cache_position += 1;
+            *filled += 1;
+        }
+    }
 }
 
 int g_step_use_whole = 1;  // lemoq_set_tuning key 4: run the step as one cooperative kernel when the shapes allow it
@@ -266,6 +277,8 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.token = d.token; p.cache_position = d.cache_position; p.filled = d.filled_len;
         p.logits = reinterpret_cast<__half*>(d.logits);
         p.next_token = d.next_token;
+        p.self_feed = d.self_feed != 0 && d.next_token != nullptr;
+        p.token_log = d.token_log;
         p.L = s->whole_layers;
         p.err_flag = s->err_flag; p.bar_counter = s->bar_counter; p.bar_epoch = s->bar_epoch;
         p.qkv = s->qkv; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
@@ -413,8 +426,10 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
     if (d.next_token != nullptr) {
         LaunchCfg plain = lc;
         plain.pdl = false;
+        const bool feed = d.self_feed != 0;
         if (int rc = launch_kernel(greedy_pick_kernel, dim3(1), dim3(1024), 0, plain, reinterpret_cast<const __half*>(d.logits), d.vocab,
-                                   d.next_token))
+                                   d.next_token, feed ? const_cast<int64_t*>(d.token) : static_cast<int64_t*>(nullptr),
+                                   const_cast<int64_t*>(d.cache_position), const_cast<int32_t*>(d.filled_len), d.token_log, d.max_len))
             return rc;
     }
     if (launches) *launches = count;

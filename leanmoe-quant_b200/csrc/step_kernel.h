@@ -32,6 +32,8 @@ struct StepParams {
     const int32_t* filled;
     __half* logits;
     int64_t* next_token;  // optional: argmax(logits)
+    int64_t* token_log;   // optional: token_log[position] = the pick
+    int self_feed;        // the step ends by making its pick the next step's input (token, position + 1, length + 1)
     const StepLayer* L;   // device array: the layers, then a pseudo layer whose q.k.v rows are the lm_head
     int* err_flag;
     unsigned int *bar_counter, *bar_epoch;

@@ -1242,7 +1242,18 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 bi = oi;
             }
         }
-        if (lane == 0) *p.next_token = (bi >= 0 && bi < p.V) ? bi : 0;
+        if (lane == 0) {
+            const int64_t pick = (bi >= 0 && bi < p.V) ? bi : 0;
+            *p.next_token = pick;
+            if (p.token_log != nullptr) p.token_log[geo.pos] = pick;
+            if (p.self_feed) {
+                // every block read the three step scalars before its first grid barrier, long ago: the next launch
+                // finds the picked token, the next slot and the next length
+                *const_cast<int64_t*>(p.token) = pick;
+                *const_cast<int64_t*>(p.cache_position) += 1;
+                *const_cast<int32_t*>(p.filled) += 1;
+            }
+        }
     }
     if (b == 0 && tid == 0) atomicAdd(p.bar_epoch, 1u);
 }

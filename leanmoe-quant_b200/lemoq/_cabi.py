@@ -39,7 +39,7 @@ class StepDesc(Structure):
         + [(n, c_int) for n in ("norm_topk_prob", "kv_int8", "attn_splits", "use_pdl")]
         + [(n, c_void_p) for n in ("embed", "final_norm", "lm_head_codes", "lm_head_scale", "rope_cos", "rope_sin",
                                    "token", "cache_position", "filled_len", "logits", "workspace")]
-        + [("workspace_bytes", c_size_t), ("next_token", c_void_p)]
+        + [("workspace_bytes", c_size_t), ("next_token", c_void_p), ("self_feed", c_int), ("token_log", c_void_p)]
     )
 
 

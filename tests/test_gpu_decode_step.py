@@ -372,6 +372,43 @@ def _full_model_greedy(ctx, expect_kernels, kv_int8=True, steps=32):
 
 
 @pytest.mark.parametrize("whole", [True, False])
+def test_chained_replays_equal_host_driven_replays(whole):
+    """K replays with no host work in between (the step feeds itself: its pick, the next slot and the next length go
+    into its own input scalars) give the tokens of K rounds of set-inputs / replay / read-back, token for token."""
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+    from lemoq import _cabi
+
+    _cabi.call("lemoq_set_tuning", 4, 1 if whole else 0)
+    try:
+        spec = _small_whole_step_spec()
+        ctx, new = 40, 24
+        wf = glue.random_float_weights(spec, seed=9, dtype=torch.float16, std=0.05, norm_weight_jitter=0.1)
+        model = lemoq_model_from_oracle(wf)
+        install_canonical(model, ctx, new)
+        prompt = torch.tensor([[(13 * i + 1) % spec.vocab for i in range(ctx)]], device=DEV)
+        session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=new, engine="step")
+        session.capture(warmup=1)
+        assert (session.capture_info["kernels_per_step"] == 1) == whole
+        session.reset()
+        host_driven, host_logits = [], None
+        for _ in range(new):
+            session.replay(synchronize=True)
+            host_driven.append(session.current_token_id)
+        host_logits = session.logits_cpu().clone()
+        session.reset()
+        chained = session.replay_chained(10) + session.replay_chained(new - 10)
+        assert chained == host_driven
+        assert session.position == ctx + new and session.current_token_id == host_driven[-1]
+        assert torch.equal(session.logits_cpu(), host_logits)
+        assert session.step_error_flags() == 0
+        with pytest.raises(RuntimeError, match="exceeded StaticCache capacity"):
+            session.replay_chained(1)
+        session.close()
+    finally:
+        _cabi.call("lemoq_set_tuning", 4, 1)
+
+
+@pytest.mark.parametrize("whole", [True, False])
 def test_out_of_range_step_scalars_raise_flags_instead_of_faulting(whole):
     """A position / length beyond the cache capacity is clamped by the kernels and reported through the flag
     word (LEMOQ_FLAG_BAD_POSITION = 1, LEMOQ_FLAG_BAD_LENGTH = 2); nothing is written outside the caches."""
