@@ -42,13 +42,17 @@ struct lemoq_step {
     unsigned int* bar_epoch;
     lemoq::StepLayer* whole_layers;  // device copy of the layer descriptors
     int whole_grid;                  // blocks of the whole-step kernel; 0 = chained kernels
-    float* stats;                   // per-block sums of squares of the q / k rows (tile form)
+    unsigned long long* flagged;    // flagged-word exchange buffers of the whole-step kernel
     unsigned long long* stamps;     // phase time stamps of the whole-step kernel
 };
 
 namespace lemoq {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// words of the flagged exchange buffers: x 4*2048, q.k.v 2*6144, sums of squares 2*2048, logits 2*128, activations 2*4096
+constexpr size_t kFlX = 0, kFlQkv = kFlX + 4 * 2048, kFlStats = kFlQkv + 2 * 6144, kFlLogits = kFlStats + 2 * 2048,
+                 kFlAct = kFlLogits + 2 * 128, kFlaggedWords = kFlAct + 2 * 4096;
 
 static int resolve_splits(const lemoq_step_desc& d) {
     if (d.attn_splits > 0) return d.attn_splits;
@@ -94,7 +98,7 @@ static size_t carve(const lemoq_step_desc& d, int splits, lemoq_step* s) {
     LEMOQ_TAKE(top_w, __half*, sizeof(__half) * d.top_k);
     LEMOQ_TAKE(top_i, int64_t*, sizeof(int64_t) * d.layers * d.top_k);
     LEMOQ_TAKE(attn_part, float*, sizeof(float) * d.heads * splits * (d.head_dim + 2));
-    LEMOQ_TAKE(stats, float*, sizeof(float) * 2 * 1024);
+    LEMOQ_TAKE(flagged, unsigned long long*, sizeof(unsigned long long) * kFlaggedWords);
     LEMOQ_TAKE(bar_counter, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(bar_epoch, unsigned int*, sizeof(unsigned int));
     LEMOQ_TAKE(whole_layers, lemoq::StepLayer*, sizeof(lemoq::StepLayer) * (d.layers + 1));
@@ -281,10 +285,10 @@ extern "C" int lemoq_step_run(lemoq_step* s, void* stream, int* launches) {
         p.token_log = d.token_log;
         p.L = s->whole_layers;
         p.err_flag = s->err_flag; p.bar_counter = s->bar_counter; p.bar_epoch = s->bar_epoch;
-        p.qkv = s->qkv; p.xa = s->xa; p.xb = s->xb; p.act = s->act;
+        p.fl_x = s->flagged + kFlX; p.fl_qkv = s->flagged + kFlQkv; p.fl_stats = s->flagged + kFlStats;
+        p.fl_logits = s->flagged + kFlLogits; p.fl_act = s->flagged + kFlAct;
         p.router_logits = s->router_logits; p.top_w = s->top_w; p.top_i = s->top_i; p.attn_part = s->attn_part;
-        p.stats = s->stats;
-        p.barriers_per_launch = 6 * d.layers + 1;
+        p.barriers_per_launch = d.layers + 1;  // attention -> o_proj in every layer, and the end of the step
         p.stamps = s->stamps;
         if (int rc = launch_step_tile(p, s->whole_grid, static_cast<cudaStream_t>(stream))) return rc;
         if (launches) *launches = 1;

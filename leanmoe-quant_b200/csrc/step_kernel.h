@@ -37,7 +37,11 @@ struct StepParams {
     const StepLayer* L;   // device array: the layers, then a pseudo layer whose q.k.v rows are the lm_head
     int* err_flag;
     unsigned int *bar_counter, *bar_epoch;
-    __half *qkv, *xa, *xb, *act, *router_logits, *top_w;
+    __half *router_logits, *top_w;
+    // flagged-word buffers (8-byte words {data, tag}), two parities each: layer outputs [2][2048] then post-attention
+    // streams [2][2048]; q.k.v rows [2][3*2048]; q/k sums of squares per block [2][2][1024]; router logits [2][128];
+    // expert activations, two per word [2][4096]
+    unsigned long long *fl_x, *fl_qkv, *fl_stats, *fl_logits, *fl_act;
     int64_t* top_i;
     float* attn_part;            // (m, l, acc[D]) partial of every (head, split) unit; at the end the per-block greedy candidates
     float* stats;                // per-block sums of squares of the q rows, then of the k rows (2 x grid floats)

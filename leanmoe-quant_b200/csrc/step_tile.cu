@@ -81,6 +81,45 @@ __device__ __forceinline__ uint2 ld_cg8(const void* p) {
     asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
+// ---- flagged words: how the blocks hand small vectors to each other without a grid barrier --------------------
+// A value travels as one 8-byte word {32 bits of data, 32-bit tag}; the tag is the sequence number of the layer
+// (unique over launches).  8-byte accesses are single-copy atomic, so a reader that sees the tag it waits for (or
+// a later one) holds the data that was stored with it: it polls the very words it needs and starts as soon as
+// they are there - one memory round trip behind the producer's store, where a barrier costs an arrival, a poll
+// and then the load.  Buffers alternate with the layer's parity; the one grid barrier per layer that remains
+// (attention -> o_proj) keeps every block within one layer of every other, so no word is overwritten while
+// somebody still waits for its previous content.
+constexpr uint32_t kFlagSpinLimit = 1u << 21;
+__device__ __forceinline__ void flag_store(unsigned long long* p, uint32_t data, uint32_t tag) {
+    const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | data;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long flag_load(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ bool tag_reached(unsigned long long w, uint32_t tag) {
+    return static_cast<int>(static_cast<uint32_t>(w >> 32) - tag) >= 0;
+}
+// N words of this thread (src[0..N), used where on[i]) until all carry the tag: data[i] = their data.  Bounded.
+template <int N>
+__device__ __forceinline__ bool flag_wait(const unsigned long long* src, const bool (&on)[N], uint32_t tag, uint32_t (&data)[N]) {
+    for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+        unsigned long long w[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) w[i] = on[i] ? flag_load(src + i) : (static_cast<unsigned long long>(tag) << 32);
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            ok = ok && tag_reached(w[i], tag);
+            data[i] = static_cast<uint32_t>(w[i]);
+        }
+        if (ok) return true;
+    }
+    return false;
+}
+
 // Block barrier of the consumer warps (the producer warps never take part in it).
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 // D = A (16x32 s8, rows) x B (32x8 s8, columns) + D, int32 accumulate.
@@ -488,19 +527,39 @@ __device__ __forceinline__ void stage_release(uint32_t empty_bar) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// routing: softmax + top-k of the E fp16 logits (E <= 128) by one warp.  Probabilities are positive
+// routing: softmax + top-k of the E fp16 logits (E <= 128, flagged words) by one warp.  Probabilities are positive
 // floats, so their bit patterns order like unsigned integers: a warp-wide integer maximum plus a ballot
 // gives the largest probability and its lowest index per round.
 // ---------------------------------------------------------------------------------------------
 template <int PER>  // experts per lane: 2 for E <= 64, 4 for E <= 128
-__device__ __forceinline__ void warp_topk_per(const __half* __restrict__ logits, int E, int K, bool norm, int lane, int& id_reg, float& w_reg) {
+__device__ __forceinline__ void warp_topk_per(const unsigned long long* logits, uint32_t tag, int* err_flag, int E, int K, bool norm,
+                                              int lane, int& id_reg, float& w_reg) {
     float v[PER];
     float mx = -INFINITY;
+    {
+        uint32_t d[PER];
+        bool on[PER];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const int e = lane + 32 * j;
-        v[j] = e < E ? __half2float(__ldcg(logits + e)) : -INFINITY;
-        mx = fmaxf(mx, v[j]);
+        for (int j = 0; j < PER; ++j) on[j] = lane + 32 * j < E;
+        // lane-strided words: word j of this lane sits 32 words further
+        bool good = true;
+        for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+            good = true;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const unsigned long long w = on[j] ? flag_load(logits + lane + 32 * j) : (static_cast<unsigned long long>(tag) << 32);
+                good = good && tag_reached(w, tag);
+                d[j] = static_cast<uint32_t>(w);
+            }
+            if (good) break;
+        }
+        if (!good && err_flag) atomicOr(err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            v[j] = on[j] ? __half2float(__ushort_as_half(static_cast<unsigned short>(d[j] & 0xffffu))) : -INFINITY;
+            mx = fmaxf(mx, v[j]);
+        }
     }
     mx = warp_max(mx);
     float sum = 0.f;
@@ -544,9 +603,10 @@ __device__ __forceinline__ void warp_topk_per(const __half* __restrict__ logits,
     if (norm) w_reg = w_reg / wsum;
     w_reg = __half2float(__float2half_rn(w_reg));  // the routing weights are used in fp16
 }
-__device__ __noinline__ void warp_topk(const __half* __restrict__ logits, int E, int K, bool norm, int lane, int& id_reg, float& w_reg) {
-    if (E <= 64) warp_topk_per<2>(logits, E, K, norm, lane, id_reg, w_reg);
-    else warp_topk_per<4>(logits, E, K, norm, lane, id_reg, w_reg);
+__device__ __noinline__ void warp_topk(const unsigned long long* logits, uint32_t tag, int* err_flag, int E, int K, bool norm, int lane,
+                                       int& id_reg, float& w_reg) {
+    if (E <= 64) warp_topk_per<2>(logits, tag, err_flag, E, K, norm, lane, id_reg, w_reg);
+    else warp_topk_per<4>(logits, tag, err_flag, E, K, norm, lane, id_reg, w_reg);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -555,20 +615,55 @@ __device__ __noinline__ void warp_topk(const __half* __restrict__ logits, int E,
 // ngroups groups of 128 fp16 values (contiguous at src; vectors of K values each) -> plane segments (vector v at
 // planes + v * 6 * (K/2 + 64)) and group scales sx[group].  With nw (one vector of at most 2048 values) the values
 // are RMS-normalised first; xh, when given, receives them as fp16 in quarters.  A half warp handles a group (eight
-// values per lane), the block twenty groups per pass; the next pass's values are requested before the current
-// ones are worked on.
-__device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, const __half* __restrict__ nw, int K, int ngroups,
-                                     unsigned char* planes, float* sx, unsigned char* xh, float* red) {
+// values per lane), the block twenty groups per pass (at most four passes, all requested before any is worked on).
+// The values come from a plain fp16 vector (src) or from flagged words (fsrc: `pack` values per word, waited for
+// until they carry `tag`).
+__device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, const unsigned long long* fsrc, uint32_t tag, int pack,
+                                     const __half* __restrict__ nw, int K, int ngroups, unsigned char* planes, float* sx,
+                                     unsigned char* xh, float* red, int* err_flag) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, lane16 = lane & 15;
-    constexpr int kPerPass = 2 * kStreamWarps;
-    int gi = warp * 2 + (lane >> 4);
-    uint4 cur = gi < ngroups ? ld_cg16(src + gi * 128 + lane16 * 8) : make_uint4(0u, 0u, 0u, 0u);
+    constexpr int kPerPass = 2 * kStreamWarps, kMaxPass = 4;
+    const int gi0 = warp * 2 + (lane >> 4);
+    // the raw fp16 values of this half warp's groups (pass q: group gi0 + 20 q), eight per lane
+    uint4 raw[kMaxPass];
+    bool good = true;
+    if (fsrc == nullptr) {  // plain fp16 vector (the embedding row)
+#pragma unroll
+        for (int q = 0; q < kMaxPass; ++q) {
+            const int gi = gi0 + q * kPerPass;
+            raw[q] = gi < ngroups ? *reinterpret_cast<const uint4*>(src + gi * 128 + lane16 * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    } else if (pack == 1) {  // one value per flagged word
+#pragma unroll
+        for (int q = 0; q < kMaxPass; ++q) {
+            const int gi = gi0 + q * kPerPass;
+            uint32_t d[8];
+            const bool act = gi < ngroups;
+            const bool on[8] = {act, act, act, act, act, act, act, act};
+            good = flag_wait<8>(fsrc + (act ? gi : 0) * 128 + lane16 * 8, on, tag, d) && good;
+            raw[q] = make_uint4((d[0] & 0xffffu) | (d[1] << 16), (d[2] & 0xffffu) | (d[3] << 16), (d[4] & 0xffffu) | (d[5] << 16),
+                                (d[6] & 0xffffu) | (d[7] << 16));
+            if (q == 0 && ngroups <= kPerPass) break;
+        }
+    } else {  // two values per flagged word
+#pragma unroll
+        for (int q = 0; q < kMaxPass; ++q) {
+            const int gi = gi0 + q * kPerPass;
+            uint32_t d[4];
+            const bool act = gi < ngroups;
+            const bool on[4] = {act, act, act, act};
+            good = flag_wait<4>(fsrc + (act ? gi : 0) * 64 + lane16 * 4, on, tag, d) && good;
+            raw[q] = make_uint4(d[0], d[1], d[2], d[3]);
+        }
+    }
+    if (!good && err_flag) atomicOr(err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+    __syncwarp();
     uint4 wv = make_uint4(0u, 0u, 0u, 0u);
     float rstd = 0.f;
     if (nw != nullptr) {  // one pass: at most 16 groups
-        if (gi < ngroups) wv = *reinterpret_cast<const uint4*>(nw + gi * 128 + lane16 * 8);
+        if (gi0 < ngroups) wv = *reinterpret_cast<const uint4*>(nw + gi0 * 128 + lane16 * 8);
         float xf[8];
-        unpack8_h(cur, xf);
+        unpack8_h(gi0 < ngroups ? raw[0] : make_uint4(0u, 0u, 0u, 0u), xf);
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss = fmaf(xf[j], xf[j], ss);
@@ -581,10 +676,11 @@ __device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, 
         rstd = 1.0f / sqrtf(tot / static_cast<float>(K) + eps);
     }
     const int kshift = 31 - __clz(K);
-#pragma unroll 1
-    for (int g0 = 0; g0 < ngroups; g0 += kPerPass, gi += kPerPass) {
-        const uint4 nxt = gi + kPerPass < ngroups ? ld_cg16(src + (gi + kPerPass) * 128 + lane16 * 8) : make_uint4(0u, 0u, 0u, 0u);
-        const __half* xv = reinterpret_cast<const __half*>(&cur);
+#pragma unroll
+    for (int q = 0; q < kMaxPass; ++q) {
+        const int gi = gi0 + q * kPerPass;
+        if (q * kPerPass >= ngroups) break;
+        const __half* xv = reinterpret_cast<const __half*>(&raw[q]);
         const __half* wh = reinterpret_cast<const __half*>(&wv);
         float f[8];
 #pragma unroll
@@ -600,10 +696,9 @@ __device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, 
             h = __floats2half2_rn(f[2], f[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
             h = __floats2half2_rn(f[4], f[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
             h = __floats2half2_rn(f[6], f[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
-            const int qv = K >> 2, q = k0 >> (kshift - 2);  // values per quarter, quarter of this group
-            *reinterpret_cast<uint4*>(xh + q * (2 * qv + kPad) + (k0 - q * qv) * 2 + lane16 * 16) = o;
+            const int qv = K >> 2, qq = k0 >> (kshift - 2);  // values per quarter, quarter of this group
+            *reinterpret_cast<uint4*>(xh + qq * (2 * qv + kPad) + (k0 - qq * qv) * 2 + lane16 * 16) = o;
         }
-        cur = nxt;
     }
     consumer_sync();
 }
@@ -673,14 +768,19 @@ __device__ __noinline__ void prepare_attention_output(const StepParams& p, Smem&
 // Warp 0: q (RMSNorm over all heads, RoPE, softmax scale, digit planes).  Warp 1 / warp 2 of the block that owns
 // the new position: the new K row (norm, RoPE) / V row into the fp16 cache and, quantised, into the int8 mirror
 // and shared memory.  Lane i holds dimensions 4i .. 4i+3; the RoPE partner (d +- 64) lives 16 lanes away.
-__device__ __noinline__ void attention_prologue(const StepParams& p, const StepLayer& L, Smem& S) {
+__device__ __noinline__ void attention_prologue(const StepParams& p, const StepLayer& L, Smem& S, const unsigned long long* fqkv,
+                                                const unsigned long long* fstats, uint32_t tag) {
     constexpr int D = kHeadDim;
     AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
     const Geo& geo = S.geo;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (warp == 0 || (geo.owner && warp < 3)) {
         const int A = geo.A, h = geo.h;
-        const uint2 raw = ld_cg8(p.qkv + warp * A + h * D + lane * 4);
+        // this lane's four values of the head's q (k, v) row: flagged words written by the q.k.v phase
+        uint32_t d4[4];
+        const bool on4[4] = {true, true, true, true};
+        bool good = flag_wait<4>(fqkv + warp * A + h * D + lane * 4, on4, tag, d4);
+        const uint2 raw = make_uint2((d4[0] & 0xffffu) | (d4[1] << 16), (d4[2] & 0xffffu) | (d4[3] << 16));
         const __half* rh = reinterpret_cast<const __half*>(&raw);
         float f[4];
         if (warp < 2) {
@@ -688,7 +788,27 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
             const __half* wh = reinterpret_cast<const __half*>(&wv);
             // sum of squares of the whole q (k) row: one partial per block of the grid, added in a fixed order
             float s = 0.f;
-            for (int b = lane; b < geo.G; b += 32) s += __ldcg(p.stats + warp * geo.G + b);
+#pragma unroll 1
+            for (int b0 = 0; b0 < geo.G; b0 += 128) {
+                uint32_t d[4];
+                bool on[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) on[i] = b0 + lane + 32 * i < geo.G;
+                for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+                    bool ok = true;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const unsigned long long w = on[i] ? flag_load(fstats + warp * 1024 + b0 + lane + 32 * i) : (static_cast<unsigned long long>(tag) << 32);
+                        ok = ok && tag_reached(w, tag);
+                        d[i] = static_cast<uint32_t>(w);
+                    }
+                    if (ok) break;
+                    if (it + 1 == kFlagSpinLimit) good = false;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s += on[i] ? __uint_as_float(d[i]) : 0.f;
+            }
+            __syncwarp();
             s = warp_sum(s);
             const float rstd = 1.0f / sqrtf(s / static_cast<float>(A) + p.eps);
 #pragma unroll
@@ -699,9 +819,11 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
                 f[j] = __half2float(__float2half_rn(__fadd_rn(__fmul_rn(x, S.cs[4 * lane + j]), __fmul_rn(rot, S.cs[D + 4 * lane + j]))));
             }
         } else {
+            __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j) f[j] = __half2float(rh[j]);
         }
+        if (!good && p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
         if (warp == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) f[j] *= p.qk_scale_log2;
@@ -976,9 +1098,10 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
     int cbase = 0;  // the same place for the phase being worked on
     unsigned char* const my_stage = S.ring + static_cast<size_t>(warp) * kStageBytes;
 
-    unsigned int bar_target = ld_acquire_u32(p.bar_epoch) * static_cast<unsigned int>(p.barriers_per_launch) * gridDim.x;
-    stamp(p, 0);
-    const __half* x_prev = p.embed + tok * static_cast<int64_t>(p.H);
+    const uint32_t epoch = ld_acquire_u32(p.bar_epoch);
+    unsigned int bar_target = epoch * static_cast<unsigned int>(p.barriers_per_launch) * gridDim.x;
+    const uint32_t tag0 = epoch * 64u;  // tag of layer l's exchanges: tag0 + l + 1 (at most 33 layers per launch)
+    const __half* const embed_row = p.embed + tok * static_cast<int64_t>(p.H);
     float pw1v[4], pw2v[4];
     plane_weights(t, true, pw1v);
     plane_weights(t, false, pw2v);
@@ -989,34 +1112,47 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
     int l = 0, ph = 0;  // phase: 0 q.k.v / lm_head, 1 attention, 2 o_proj, 3 router, 4 gate/up, 5 down
     const int nphases = 6 * p.layers + 1;
 
-#pragma unroll 1
-    for (int step = 0; step <= nphases; ++step) {
-        // ---- grid barrier behind the previous phase --------------------------------------------------------
-        if (step > 0) {
-            if (tid == 0) {
-                unsigned int n = 0;
-                while (static_cast<int>(ld_acquire_u32(p.bar_counter) - bar_target) < 0) {
-                    if (++n > kBarrierSpinLimit) {
-                        if (p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
-                        break;
-                    }
+    auto grid_arrive = [&]() {  // after a block barrier: the writes of the whole block are ordered before the arrival
+        bar_target += gridDim.x;
+        if (tid == 0) red_release_add(p.bar_counter, 1u);
+    };
+    auto grid_wait = [&]() {
+        if (tid == 0) {
+            unsigned int n = 0;
+            while (static_cast<int>(ld_acquire_u32(p.bar_counter) - bar_target) < 0) {
+                if (++n > kBarrierSpinLimit) {
+                    if (p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
+                    break;
                 }
             }
-            consumer_sync();
-            stamp(p, step);
         }
-        if (step == nphases) break;
+        consumer_sync();
+    };
+
+#pragma unroll 1
+    for (int step = 0; step < nphases; ++step) {
+        stamp(p, step);
         const StepLayer& L = S.layers[l];
         const bool last = l == p.layers;
         const int ntiles = last ? geo.nt[6] : geo.nt[ph];
         const int lt0 = warp - cbase + (warp < cbase ? kStreamWarps : 0);  // this warp's first tile of the phase
         cbase = (cbase + ntiles) % kStreamWarps;
+        // flagged-word buffers of this layer (parity l & 1) and of the previous layer's output
+        const int par = l & 1, ppar = par ^ 1;
+        const uint32_t tag = tag0 + l + 1;
+        unsigned long long* const f_x2 = p.fl_x + par * 2048;            // this layer's output (down phase)
+        const unsigned long long* const f_xin = p.fl_x + ppar * 2048;    // the previous layer's output
+        unsigned long long* const f_xa = p.fl_x + (2 + par) * 2048;      // residual stream after attention
+        unsigned long long* const f_qkv = p.fl_qkv + par * 3 * 2048;
+        unsigned long long* const f_stats = p.fl_stats + par * 2048;
+        unsigned long long* const f_logits = p.fl_logits + par * 128;
+        unsigned long long* const f_act = p.fl_act + par * 4096;
         float sq = 0.f, sk = 0.f;  // phase A: sums of squares of the q / k values this lane stored
 
         if (ph == 1) {
             if (geo.has_unit) {
                 AttnSm& sm = *reinterpret_cast<AttnSm*>(S.big);
-                attention_prologue(p, L, S);
+                attention_prologue(p, L, S, f_qkv, f_stats, tag);
                 {
                     float m_i = -INFINITY, l_i = 0.f;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1047,35 +1183,36 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 consumer_sync();
                 attention_partial(p, S);
             }
+            // the one grid barrier of the layer: the o_proj phase of every block merges the partials of all units
+            consumer_sync();
+            grid_arrive();
         } else {
             // ---- block-wide preparation of the phase -----------------------------------------------------
             if (ph == 4) {
                 if (warp == 0) {  // one warp routes, the others pick the result up from shared memory
                     int id;
                     float w;
-                    warp_topk(p.router_logits + static_cast<int64_t>(l) * p.E, p.E, p.K, p.norm_topk != 0, lane, id, w);
+                    warp_topk(f_logits, tag, p.err_flag, p.E, p.K, p.norm_topk != 0, lane, id, w);
                     S.route_id[lane] = id;
                     S.route_w[lane] = lane < p.K ? w : 0.f;
                     if (b == 0 && lane < p.K) {
                         p.top_i[static_cast<int64_t>(l) * p.K + lane] = id;
                         p.top_w[lane] = __float2half_rn(w);
                     }
-                }
-                if (warp == 0) {
                     __threadfence_block();
                     if (lane == 0) S.ready_layer = l;  // the producers may start the expert tiles of this layer
                 }
                 consumer_sync();
             } else if (ph == 2) {
+                grid_wait();
                 prepare_attention_output(p, S);
+            } else if (ph == 0) {
+                prepare(p.eps, embed_row, l == 0 ? nullptr : f_xin, tag - 1, 1, L.ln1, p.H, p.H >> 7, S.xplanes, S.xsx, nullptr, S.red, p.err_flag);
+            } else if (ph == 3) {
+                prepare(p.eps, nullptr, f_xa, tag, 1, L.ln2, p.H, p.H >> 7, S.xplanes, S.xsx, S.xh, S.red, p.err_flag);
             } else {
-                const int K = ph == 5 ? p.F : p.H;
-                prepare(p.eps, ph == 0 ? x_prev : (ph == 3 ? p.xa : p.act), ph == 0 ? L.ln1 : (ph == 3 ? L.ln2 : nullptr), K,
-                        ph == 5 ? (p.K * p.F) >> 7 : K >> 7, ph == 5 ? S.big : S.xplanes, ph == 5 ? fsx : S.xsx, ph == 3 ? S.xh : nullptr, S.red);
+                prepare(p.eps, nullptr, f_act, tag, 2, nullptr, p.F, (p.K * p.F) >> 7, S.big, fsx, nullptr, S.red, p.err_flag);
             }
-            // the residual of this thread's down row (in flight while the tiles are worked on)
-            __half resid_f = __float2half_rn(0.f);
-            if (ph == 5 && tid < geo.f_blocks * 8) resid_f = __ldcg(p.xa + (b + (tid >> 3) * G) * 8 + (tid & 7));
             // ---- this warp's tiles of the phase: a warp finishes the rows of its tile by itself ------------------
             {
                 const int K = ph == 2 ? A : (ph == 5 ? p.F : p.H);
@@ -1083,7 +1220,10 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 for (int lt = lt0; lt < ntiles; lt += kStreamWarps) {
                     const int tg = b + lt * G;  // global tile index (not in the down phase)
                     __half resid = __float2half_rn(0.f);
-                    if (ph == 2) resid = __ldcg(x_prev + tg * 8 + g);  // in flight while the tile is worked on
+                    if (ph == 2) {  // the residual of this lane's row (this block has seen the tag of every word in phase A)
+                        const int n = tg * 8 + g;
+                        resid = l == 0 ? embed_row[n] : __ushort_as_half(static_cast<unsigned short>(flag_load(f_xin + n) & 0xffffu));
+                    }
                     if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
                     c_par ^= 1u;
                     float val;
@@ -1120,7 +1260,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         const float f = __half2float(hv);
                         if (t == 0) {
                             if (!last) {
-                                p.qkv[n] = hv;
+                                flag_store(f_qkv + n, __half_as_ushort(hv), tag);
                                 if (n < A) sq = fmaf(f, f, sq);
                                 else if (n < 2 * A) sk = fmaf(f, f, sk);
                             } else {
@@ -1132,21 +1272,26 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                             }
                         }
                     } else if (ph == 2) {
-                        if (t == 0) p.xa[tg * 8 + g] = __hadd(__float2half_rn(val), resid);
+                        if (t == 0) flag_store(f_xa + tg * 8 + g, __half_as_ushort(__hadd(__float2half_rn(val), resid)), tag);
                     } else if (ph == 3) {
                         const int e = tg * 4 + g;
-                        if (t == 0 && g < 4 && e < p.E) p.router_logits[static_cast<int64_t>(l) * p.E + e] = __float2half_rn(val);
+                        if (t == 0 && g < 4 && e < p.E) {
+                            const __half hv = __float2half_rn(val);
+                            flag_store(f_logits + e, __half_as_ushort(hv), tag);
+                            p.router_logits[static_cast<int64_t>(l) * p.E + e] = hv;  // kept for inspection
+                        }
                     } else if (ph == 4) {
                         const float up = __shfl_down_sync(0xffffffffu, val, 16);  // rows 4-7 of the tile are the up rows
+                        const uint32_t mine = __half_as_ushort(__float2half_rn(val * (1.0f / (1.0f + expf(-val))) * up));
+                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 4);  // the activation of the next row
                         const int slot = tg >> geo.shF4, n = ((tg - (slot << geo.shF4)) << 2) + g;
-                        if (t == 0 && g < 4) p.act[slot * p.F + n] = __float2half_rn(val * (1.0f / (1.0f + expf(-val))) * up);
+                        if (t == 0 && (g == 0 || g == 2)) flag_store(f_act + ((slot * p.F + n) >> 1), mine | (next << 16), tag);  // two per word
                     }
                 }
             }
             if (ph == 5) {
                 // the routed experts of a down row are consecutive tiles: routing-weighted sum in slot order
                 const int nrows = geo.f_blocks * 8;
-                __half resid = resid_f;
                 consumer_sync();
 #pragma unroll 1
                 for (int i = tid; i < nrows; i += kConsumerThreads) {
@@ -1155,8 +1300,9 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
 #pragma unroll 1
                     for (int slot = 0; slot < p.K; ++slot) out = fmaf(S.route_w[slot], S.part[(j * p.K + slot) * 8 + r], out);
                     const int n = (b + j * G) * 8 + r;
-                    if (i >= kConsumerThreads) resid = __ldcg(p.xa + n);
-                    p.xb[n] = __hadd(__float2half_rn(out), resid);
+                    // the residual: this block has seen the tag of every word of the stream in the router phase
+                    const __half resid = __ushort_as_half(static_cast<unsigned short>(flag_load(f_xa + n) & 0xffffu));
+                    flag_store(f_x2 + n, __half_as_ushort(__hadd(__float2half_rn(out), resid)), tag);
                 }
             } else if (ph == 0) {
                 if (!last) {
@@ -1182,45 +1328,44 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     }
                 }
             }
-        }
-        // ---- arrive at the grid barrier of this phase ------------------------------------------------------------
-        consumer_sync();
-        bar_target += gridDim.x;
-        if (tid == 0) {
-            if (ph == 0 && !last) {
-                // this block's share of the sums of squares of the q and k rows (its rows as stored, in fp16)
-                float a = 0.f, c = 0.f;
-                for (int w = 0; w < kStreamWarps; ++w) {
-                    a += S.red[w];
-                    c += S.red[kWarps + w];
-                }
-                p.stats[b] = a;
-                p.stats[G + b] = c;
-            } else if (ph == 0 && p.next_token != nullptr) {
-                // this block's candidate for the greedy pick
-                float best = S.red[0];
-                int bi = reinterpret_cast<int*>(S.red)[kWarps];
-                for (int w = 1; w < kStreamWarps; ++w) {
-                    const float v = S.red[w];
-                    const int i = reinterpret_cast<int*>(S.red)[kWarps + w];
-                    if (better(v, i, best, bi)) {
-                        best = v;
-                        bi = i;
+            // ---- end of the phase: the block's shared buffers are free again ----------------------------------------
+            consumer_sync();
+            if (ph == 0 && tid == 0) {
+                if (!last) {
+                    // this block's share of the sums of squares of the q and k rows (its rows as stored, in fp16)
+                    float a = 0.f, c = 0.f;
+                    for (int w = 0; w < kStreamWarps; ++w) {
+                        a += S.red[w];
+                        c += S.red[kWarps + w];
                     }
+                    flag_store(f_stats + b, __float_as_uint(a), tag);
+                    flag_store(f_stats + 1024 + b, __float_as_uint(c), tag);
+                } else if (p.next_token != nullptr) {
+                    // this block's candidate for the greedy pick
+                    float best = S.red[0];
+                    int bi = reinterpret_cast<int*>(S.red)[kWarps];
+                    for (int w = 1; w < kStreamWarps; ++w) {
+                        const float v = S.red[w];
+                        const int i = reinterpret_cast<int*>(S.red)[kWarps + w];
+                        if (better(v, i, best, bi)) {
+                            best = v;
+                            bi = i;
+                        }
+                    }
+                    p.attn_part[2 * b] = best;
+                    p.attn_part[2 * b + 1] = __int_as_float(bi);
                 }
-                p.attn_part[2 * b] = best;
-                p.attn_part[2 * b + 1] = __int_as_float(bi);
             }
-            // release at gpu scope is cumulative: it orders the writes of the whole block, which the block barrier
-            // above made visible to this thread, before the arrival
-            red_release_add(p.bar_counter, 1u);
+            if (last) grid_arrive();  // the logits and this block's candidate are out
         }
         if (++ph == 6) {
             ph = 0;
             ++l;
-            x_prev = p.xb;
         }
     }
+    stamp(p, nphases);
+    if (b != 0) return;
+    grid_wait();  // block 0 ends the step: every block has delivered its logits and its candidate
     if (p.next_token != nullptr && b == 0 && warp == 0) {
         // greedy pick on the device: one candidate per block (written before the last barrier), merged here
         float best = -INFINITY;
