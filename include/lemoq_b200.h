@@ -148,7 +148,9 @@ LEMOQ_API int lemoq_kv_int8_cache_write(const void* k_row, const void* v_row, in
                               const int64_t* pos, int heads, int S, int D, int* err_flag, void* stream);
 
 /* Bulk quantisation of a whole fp16 cache into the mirror; slots at or beyond
- * `filled` get code 0 / scale 1 (filled < 0 quantises every slot).
+ * `filled` get code 0 / scale 1 (filled < 0 quantises every slot; filled == 0
+ * writes code 0 / scale 1 everywhere).  The reference's Python function treats a
+ * zero length like "no length" (kv_int8.py:147); the host mirror passes -1 for it.
  * ref: src/lemoq/kernels/kv_int8.py:127 (kv_int8_bulk_quantize).
  */
 LEMOQ_API int lemoq_kv_int8_bulk_quantize(const void* keys, const void* values, int8_t* kc, void* ks, int8_t* vc, void* vs,
@@ -335,8 +337,9 @@ LEMOQ_API const void* lemoq_step_router_logits(lemoq_step* step);
  * int8 tensor-core dot product) or "chained" (6 kernels per layer).  Static string.  No counterpart in the
  * reference (ref for the step itself: benchmarks/cudagraph.py:713). */
 LEMOQ_API const char* lemoq_step_engine(lemoq_step* step);
-/* Device pointer to 6*layers + 2 global-timer stamps (ns) taken by the whole-step kernel at its start and
- * after each phase barrier of the last step; NULL when the step runs as chained kernels. */
+/* Device pointer to 6*layers + 2 global-timer stamps (ns) of the last step, taken by block 0 of the whole-step
+ * kernel: at its start, where it begins each phase of each layer (the phases of different blocks overlap, so
+ * these are one block's view), and at its end; NULL when the step runs as chained kernels. */
 LEMOQ_API const unsigned long long* lemoq_step_phase_stamps(lemoq_step* step);
 
 #define LEMOQ_FLAG_BAD_POSITION 1

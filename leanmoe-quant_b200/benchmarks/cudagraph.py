@@ -25,17 +25,24 @@ from typing import Any
 
 VALID_EXECUTIONS = ("eager", "cudagraph")
 VALID_ENGINES = ("auto", "step", "ops")
+_MIN_TIMED = 20   # a timing run never uses fewer steps than this ...
+_MIN_WARMUP = 5   # ... nor fewer warm-up steps
+_KL_GATE = 1e-5   # graph replay against the same path run eagerly
+
+
+def _one_of(value: str, allowed: tuple[str, ...], what: str) -> str:
+    if value not in allowed:
+        raise ValueError("unknown %s %r; expected one of %s" % (what, value, allowed))
+    return value
 
 
 def normalize_execution(value: str) -> str:
-    if value not in VALID_EXECUTIONS:
-        raise ValueError("unknown execution %r; expected one of %s" % (value, VALID_EXECUTIONS))
-    return value
+    return _one_of(value, VALID_EXECUTIONS, "execution")
 
 
 @dataclass(frozen=True)
 class CudaGraphConfig:
-    """Static-shape contract of one batch-1 decode graph."""
+    """The fixed shape of one batch-1 decode graph: prompt length, room for new tokens, one row, one query."""
 
     ctx: int
     max_new_tokens: int
@@ -43,33 +50,36 @@ class CudaGraphConfig:
     q_len: int = 1
 
     def __post_init__(self) -> None:
-        if self.batch != 1:
-            raise ValueError("the decode graph supports batch=1 only")
-        if self.q_len != 1:
-            raise ValueError("the decode graph supports q_len=1 only")
-        if self.ctx <= 0 or self.max_new_tokens <= 0:
-            raise ValueError("ctx and max_new_tokens must be positive")
-        if self.ctx < 2:
-            raise ValueError("ctx must be >= 2: ctx=1 routes the prefill token through the q_len=1 decode path "
-                             "with filled_len=0 (zero attention)")
+        for ok, text in (
+            (self.batch == 1, "the decode graph supports batch=1 only"),
+            (self.q_len == 1, "the decode graph supports q_len=1 only"),
+            (self.ctx > 0 and self.max_new_tokens > 0, "ctx and max_new_tokens must be positive"),
+            # with ctx=1 the prompt itself would go through the one-token path with nothing filled yet
+            (self.ctx >= 2, "ctx must be >= 2: ctx=1 routes the prefill token through the q_len=1 decode path "
+                            "with filled_len=0 (zero attention)"),
+        ):
+            if not ok:
+                raise ValueError(text)
 
     @property
     def max_cache_len(self) -> int:
         return self.ctx + self.max_new_tokens
 
     def validate_timing(self, timed: int) -> None:
+        """A timing run of ``timed`` steps (at least ``_MIN_TIMED`` are run) must fit into the room for new tokens."""
         if timed <= 0:
             raise ValueError("timed must be positive")
-        effective = max(timed, 20)
-        if effective > self.max_new_tokens:
+        run = max(timed, _MIN_TIMED)
+        if run > self.max_new_tokens:
             raise ValueError("effective timed=%d exceeds max_new_tokens=%d; StaticCache timing horizon would overflow"
-                             % (effective, self.max_new_tokens))
+                             % (run, self.max_new_tokens))
 
 
 @dataclass
 class GraphBuffers:
-    """Fixed-address step inputs.  ``filled_len`` (int32) is the device-side loop bound of the
-    attention kernel; ``cache_position`` (int64) is the slot the new K/V row is written to."""
+    """The step inputs at addresses that never change.  ``token``, ``cache_position`` (the slot the new key/value row
+    goes to), ``position_ids`` and ``filled_len`` (int32: the attention kernel's loop bound) are views of ONE
+    ``int64[4]`` array, ``packed``, so a host-driven loop updates all four with a single 32-byte copy."""
 
     token: Any
     cache_position: Any
@@ -77,7 +87,7 @@ class GraphBuffers:
     attention_mask: Any
     next_token: Any
     filled_len: Any = None
-    packed: Any = None  # int64[4] holding token, cache_position, position_ids and (low half of slot 3) filled_len
+    packed: Any = None
 
     @classmethod
     def allocate(cls, device: Any, *, batch: int, max_cache_len: int | None = None, dtype: Any | None = None) -> "GraphBuffers":
@@ -85,124 +95,116 @@ class GraphBuffers:
 
         if batch != 1:
             raise ValueError("GraphBuffers currently supports batch=1 only")
-        max_cache_len = 1 if max_cache_len is None else max_cache_len
-        dtype = torch.float32 if dtype is None else dtype
-        # The four step scalars are views of ONE 32-byte buffer, so that a caller with host-side inputs can
-        # update all of them with a single host->device copy (see pack_step()).
-        packed = torch.zeros(4, dtype=torch.long, device=device)
-        return cls(
-            token=packed[0:1].view(batch, 1),
-            cache_position=packed[1:2],
-            position_ids=packed[2:3].view(batch, 1),
-            attention_mask=torch.zeros((batch, 1, 1, max_cache_len), dtype=dtype, device=device),
-            next_token=torch.zeros((batch, 1), dtype=torch.long, device=device),
-            filled_len=packed[3:4].view(torch.int32)[0:1],
-            packed=packed,
-        )
+        words = torch.zeros(4, dtype=torch.long, device=device)
+        mask = torch.zeros((1, 1, 1, max_cache_len or 1), dtype=dtype or torch.float32, device=device)
+        return cls(token=words[0:1].view(1, 1), cache_position=words[1:2], position_ids=words[2:3].view(1, 1),
+                   attention_mask=mask, next_token=torch.zeros((1, 1), dtype=torch.long, device=device),
+                   filled_len=words[3:4].view(torch.int32)[0:1], packed=words)
 
     @staticmethod
     def pack_step(host: Any, *, token: int, position: int) -> Any:
-        """Fill a host int64[4] tensor with the image of the step scalars (little-endian int32 in slot 3)."""
-        host[0], host[1], host[2], host[3] = int(token), int(position), int(position), int(position) + 1
+        """The image of the four scalars for (``token``, ``position``) in a host ``int64[4]``: the length
+        ``position + 1`` sits in the low half of word 3 (little-endian)."""
+        for word, value in enumerate((token, position, position, position + 1)):
+            host[word] = int(value)
         return host
 
     def set_step(self, *, token: int, position: int) -> None:
         self.token.fill_(int(token))
-        self.cache_position.fill_(int(position))
-        self.position_ids.fill_(int(position))
+        for scalar in (self.cache_position, self.position_ids):
+            scalar.fill_(int(position))
         if self.filled_len is not None:
             self.filled_len.fill_(int(position) + 1)
 
     def addresses(self) -> tuple[int, ...]:
-        tensors = (self.token, self.cache_position, self.position_ids, self.attention_mask, self.next_token)
-        if self.filled_len is not None:
-            tensors = tensors + (self.filled_len,)
-        return tuple(int(t.data_ptr()) for t in tensors)
+        """Device addresses of the inputs (a replay must find them where capture saw them)."""
+        fixed = [self.token, self.cache_position, self.position_ids, self.attention_mask, self.next_token]
+        fixed += [] if self.filled_len is None else [self.filled_len]
+        return tuple(int(t.data_ptr()) for t in fixed)
 
 
 class CudaGraphCaptureError(RuntimeError):
-    """Capture/replay failure with an explicit lifecycle stage."""
+    """A failure in ``stage`` ("capture", "replay", "correctness") of the graph's life; ``cause`` is the original."""
 
     def __init__(self, stage: str, cause: BaseException):
-        self.stage = stage
-        self.cause = cause
         super().__init__("CUDA Graph %s failed: %s: %s" % (stage, type(cause).__name__, cause))
+        self.stage, self.cause = stage, cause
 
 
 class CudaGraphCorrectnessError(CudaGraphCaptureError):
     def __init__(self, report: dict[str, Any]):
+        summary = "graph/eager correctness gate failed: KL=%s top1=%s" % (report.get("kl"), report.get("top1_agreement"))
+        super().__init__("correctness", RuntimeError(summary))
         self.report = report
-        super().__init__("correctness", RuntimeError("graph/eager correctness gate failed: KL=%s top1=%s"
-                                                     % (report.get("kl"), report.get("top1_agreement"))))
 
 
 def compare_logits(reference: list[Any], candidate: list[Any]) -> dict[str, Any]:
-    """Mean over steps of ``KL(ref || got)`` in fp32 and top-1 agreement (both moved to the CPU)."""
+    """``KL(reference || candidate)`` averaged over the steps, and the share of steps with the same arg-max.
+    Computed on the CPU in fp32 whatever the inputs are."""
     import torch
 
-    if len(reference) != len(candidate) or not reference:
+    if not reference or len(reference) != len(candidate):
         raise ValueError("reference and candidate must have the same non-empty step count")
-
-    def flat(x: Any) -> Any:
-        return x.detach().reshape(1, -1).to(device="cpu", dtype=torch.float32)
-
-    ref = torch.cat([flat(x) for x in reference], dim=0)
-    got = torch.cat([flat(x) for x in candidate], dim=0)
-    ref_logp, got_logp = torch.log_softmax(ref, dim=-1), torch.log_softmax(got, dim=-1)
-    kl = (ref_logp.exp() * (ref_logp - got_logp)).sum(dim=-1).mean()
-    agreement = (ref.argmax(dim=-1) == got.argmax(dim=-1)).to(torch.float32).mean()
-    return {"kl": max(float(kl.item()), 0.0), "top1_agreement": float(agreement.item())}
+    rows = lambda steps: torch.stack([t.detach().reshape(-1).to("cpu", torch.float32) for t in steps])  # noqa: E731
+    ref, got = rows(reference), rows(candidate)
+    log_p, log_q = ref.log_softmax(-1), got.log_softmax(-1)
+    kl = torch.sum(log_p.exp() * (log_p - log_q), dim=-1).mean().item()
+    same = (ref.argmax(-1) == got.argmax(-1)).float().mean().item()
+    return {"kl": max(float(kl), 0.0), "top1_agreement": float(same)}
 
 
 def graph_correctness_passed(report: dict[str, Any]) -> bool:
+    """The gate of graph replay against eager: KL within ``_KL_GATE`` (and finite), every arg-max equal, the same seed
+    token and the same token sequence."""
     kl = report.get("kl")
-    return bool(kl is not None and math.isfinite(float(kl)) and 0.0 <= float(kl) <= 1e-5
-                and report.get("top1_agreement") == 1.0 and report.get("seed_token_match") is True
-                and report.get("token_sequence_match") is True)
+    if kl is None or not math.isfinite(float(kl)) or not 0.0 <= float(kl) <= _KL_GATE:
+        return False
+    return report.get("top1_agreement") == 1.0 and all(report.get(k) is True for k in ("seed_token_match", "token_sequence_match"))
 
 
 def replay_timed_step(session: Any) -> Any:
-    """One user-visible autoregressive step: step inputs, graph replay, sync, host argmax."""
+    """What one generated token costs a user: set the inputs, replay, synchronize, pick the next token."""
     return session.replay(synchronize=True)
 
 
 def summarize(samples: list[float]) -> dict[str, float]:
-    s = sorted(samples)
-    n = len(s)
-    return {"n": n, "p50": statistics.median(s), "p99": s[min(n - 1, int(math.ceil(0.99 * n)) - 1)], "min": s[0],
-            "max": s[-1], "mean": sum(s) / n, "stddev": statistics.pstdev(s) if n > 1 else 0.0}
+    ordered = sorted(samples)
+    count = len(ordered)
+    rank99 = min(count, max(1, math.ceil(0.99 * count)))  # nearest-rank percentile
+    return {"n": count, "p50": statistics.median(ordered), "p99": ordered[rank99 - 1], "min": ordered[0], "max": ordered[-1],
+            "mean": math.fsum(ordered) / count, "stddev": statistics.pstdev(ordered) if count > 1 else 0.0}
 
 
 def measure_graph_gap(session: Any, *, warmup: int = 5, timed: int = 20, repeats: int = 3) -> dict[str, Any]:
-    """Wall-clock and CUDA-event time per decoded token over ``repeats`` x ``timed`` graph steps,
-    each repeat starting from the prefilled state (reset outside the timed window)."""
+    """Per generated token: wall-clock and CUDA-event time of the host-driven greedy loop (``repeats`` runs of ``timed``
+    steps, each from the prefilled state, resets outside the timed window), against the device time of back-to-back
+    replays.  The difference is what the host costs."""
     torch = session.torch
-    warmup, timed = max(warmup, 5), max(timed, 20)
-    wall, event = [], []
+    warmup, timed = max(warmup, _MIN_WARMUP), max(timed, _MIN_TIMED)
+    wall_ms, event_ms = [], []
     for _ in range(repeats):
         session.reset()
         for _ in range(warmup):
             session.replay(synchronize=False)
         session.stream.synchronize()
         session.reset()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(session.stream)
-        t0 = time.perf_counter()
+        first, last = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+        first.record(session.stream)
+        began = time.perf_counter()
         for _ in range(timed):
             replay_timed_step(session)
         session.stream.synchronize()
-        wall.append((time.perf_counter() - t0) * 1000.0 / timed)
-        end.record(session.stream)
+        wall_ms.append(1e3 * (time.perf_counter() - began) / timed)
+        last.record(session.stream)
         session.stream.synchronize()
-        event.append(start.elapsed_time(end) / timed)
-    gpu_only = session.time_graph_only(iters=timed)
-    w, e = summarize(wall), summarize(event)
-    host = max(w["p50"] - gpu_only, 0.0)
+        event_ms.append(first.elapsed_time(last) / timed)
+    busy = session.time_graph_only(iters=timed)
+    wall, event = summarize(wall_ms), summarize(event_ms)
+    host = max(wall["p50"] - busy, 0.0)
     return {"status": "measured", "method": "perf_counter wall + CUDA events around the greedy loop; back-to-back replays for gpu_busy",
-            "wall_p50_ms": w["p50"], "wall_p99_ms": w["p99"], "gpu_p50_ms": e["p50"], "gpu_p99_ms": e["p99"],
-            "gpu_busy_ms": gpu_only, "host_p50_ms": host,
-            "host_share_pct": round(100.0 * host / w["p50"], 1) if w["p50"] else None,
-            "kernels_per_call": session.capture_info.get("kernels_per_step"), "stats": {"wall": w, "gpu_event": e}}
+            "wall_p50_ms": wall["p50"], "wall_p99_ms": wall["p99"], "gpu_p50_ms": event["p50"], "gpu_p99_ms": event["p99"],
+            "gpu_busy_ms": busy, "host_p50_ms": host, "host_share_pct": round(100.0 * host / wall["p50"], 1) if wall["p50"] else None,
+            "kernels_per_call": session.capture_info.get("kernels_per_step"), "stats": {"wall": wall, "gpu_event": event}}
 
 
 def _skip_mask_fill_enabled() -> bool:
@@ -220,38 +222,36 @@ class StaticCacheDecodeSession:
 
         from lemoq.model import StaticCache
 
-        if engine not in VALID_ENGINES:
-            raise ValueError("unknown engine %r; expected one of %s" % (engine, VALID_ENGINES))
-        if prompt_ids.ndim != 2 or prompt_ids.shape != (1, ctx):
+        _one_of(engine, VALID_ENGINES, "engine")
+        if tuple(prompt_ids.shape) != (1, ctx):
             raise ValueError("prompt_ids must have shape [1, ctx]")
         self.torch = torch
-        self._cuda_available = bool(torch.cuda.is_available())
-        self.model = model.eval()
-        self.prompt_ids = prompt_ids
         self.device = torch.device(device)
+        self._cuda_available = bool(torch.cuda.is_available())
         self.config = CudaGraphConfig(ctx=ctx, max_new_tokens=max_new_tokens, batch=1)
+        self.model, self.prompt_ids = model.eval(), prompt_ids
         self.dtype = next(model.parameters()).dtype
-        self.cache = StaticCache(config=model.config, max_cache_len=self.config.max_cache_len)
-        self.buffers = GraphBuffers.allocate(self.device, batch=1, max_cache_len=self.config.max_cache_len, dtype=self.dtype)
-        self.cache._lemoq_filled_len = self.buffers.filled_len
-        self.graph = None
-        self._captured_mask_independent = False
-        self.stream = None
-        self.logits = None
-        self.current_token_id: int | None = None
-        self.position = self.config.ctx
-        self.capture_info: dict[str, Any] = {"max_cache_len": self.config.max_cache_len, "q_len": 1, "batch": 1,
-                                             "capture_success": False, "replay_success": False}
-        env_engine = os.environ.get("LEMOQ_STEP_ENGINE")
-        if env_engine is not None and engine == "auto":
-            engine = "step" if env_engine == "1" else "ops"
-        self._engine_request = engine
-        self._use_pdl = (os.environ.get("LEMOQ_PDL", "1") == "1") if use_pdl is None else bool(use_pdl)
+        capacity = self.config.max_cache_len
+        self.cache = StaticCache(config=model.config, max_cache_len=capacity)
+        self.buffers = GraphBuffers.allocate(self.device, batch=1, max_cache_len=capacity, dtype=self.dtype)
+        self.cache._lemoq_filled_len = self.buffers.filled_len  # the attention modules find the device length here
+        # engine choice: an explicit argument wins; "auto" listens to LEMOQ_STEP_ENGINE (1 = step, else ops)
+        forced = os.environ.get("LEMOQ_STEP_ENGINE")
+        self._engine_request = engine if engine != "auto" or forced is None else ("step" if forced == "1" else "ops")
+        self._use_pdl = os.environ.get("LEMOQ_PDL", "1") == "1" if use_pdl is None else bool(use_pdl)
         self._attn_splits = int(attn_splits)
-        self._step = None  # native step plan (built lazily, after the first prefill)
-        self._chain_host = None  # pinned read-back buffer of replay_chained
         self.engine = None
-        self.after_prefill = None  # optional callable(session): runs at the end of every prefill
+        self._step = None         # plan of the native step engine (built after the first prefill)
+        self._chain_host = None   # pinned buffer of replay_chained
+        self.after_prefill = None  # optional callable(session), run at the end of every prefill
+        # graph state
+        self.graph = self.stream = self.logits = None
+        self._captured_mask_independent = False
+        self.capture_info: dict[str, Any] = {"max_cache_len": capacity, "q_len": 1, "batch": 1, "capture_success": False,
+                                             "replay_success": False}
+        # decode state
+        self.current_token_id: int | None = None
+        self.position = ctx
         self.prefill()
 
     # ------------------------------------------------------------------ prefill
@@ -259,28 +259,38 @@ class StaticCacheDecodeSession:
         self.cache.reset()
 
     def prefill(self) -> Any:
-        """Eagerly fill the static cache and seed the next decode token."""
-        torch = self.torch
+        """Run the prompt through the model eagerly into the emptied static cache; the arg-max of the last position
+        seeds the decode."""
+        torch, ctx = self.torch, self.config.ctx
         self._clear_cache()
-        positions = torch.arange(self.config.ctx, device=self.device, dtype=torch.long)
-        attention_mask = torch.ones((1, self.config.ctx), device=self.device, dtype=torch.long)
+        slots = torch.arange(ctx, dtype=torch.long, device=self.device)
         with torch.no_grad():
-            output = self.model(self.prompt_ids, attention_mask=attention_mask, past_key_values=self.cache, use_cache=True,
-                                cache_position=positions, position_ids=positions.unsqueeze(0))
-        self.current_token_id = int(output.logits[:, -1:, :].argmax(dim=-1).item())
-        self.position = self.config.ctx
+            output = self.model(self.prompt_ids, attention_mask=torch.ones_like(slots).unsqueeze(0), past_key_values=self.cache,
+                                use_cache=True, cache_position=slots, position_ids=slots.unsqueeze(0))
+        self.current_token_id, self.position = int(output.logits[0, -1].argmax().item()), ctx
         if self.after_prefill is not None:
             self.after_prefill(self)
         self._requantize_mirror()
-        if self._cuda_available:
-            torch.cuda.synchronize()
+        self._device_sync()
         return output
+
+    def _device_sync(self) -> None:
+        if self._cuda_available:
+            self.torch.cuda.synchronize()
+
+    def _seeded_token(self, purpose: str) -> int:
+        if self.current_token_id is None:
+            raise RuntimeError("prefill must run before %s" % purpose)
+        return self.current_token_id
+
+    def _room_for(self, steps: int = 1) -> None:
+        if self.position + steps > self.config.max_cache_len:
+            raise RuntimeError("decode position exceeded StaticCache capacity (%d + %d > %d)"
+                               % (self.position, steps, self.config.max_cache_len))
 
     @property
     def seed_token_id(self) -> int:
-        if self.current_token_id is None:
-            raise RuntimeError("prefill must run before reading the seed token")
-        return self.current_token_id
+        return self._seeded_token("reading the seed token")
 
     def buffer_addresses(self) -> tuple[int, ...]:
         return self.buffers.addresses()
@@ -514,111 +524,115 @@ class StaticCacheDecodeSession:
         return {"phases": d[: 6 * layers].reshape(layers, 6), "lm_head": float(d[6 * layers]), "total": float((st[-1] - st[0]) / 1000.0)}
 
     # ------------------------------------------------------------------ decode
+    def _adopt(self, logits: Any) -> None:
+        """Take the step's pick as the next input.  The native step engine has picked on the device (first maximal
+        logit, which is what a host arg-max returns); otherwise pick here."""
+        picked = self.step_next_token
+        self.current_token_id = int((picked if picked is not None else logits.reshape(-1).argmax()).item())
+        self.position += 1
+
     def decode_eager(self) -> Any:
-        if self.current_token_id is None:
-            raise RuntimeError("prefill must run before decode")
-        if self.position >= self.config.max_cache_len:
-            raise RuntimeError("decode position exceeded StaticCache capacity")
+        """One decode step without the graph (the comparison arm of the correctness gate)."""
         self._set_step_inputs()
         with self.torch.no_grad():
             logits = self._forward_once().detach()
+        self._device_sync()
         self.current_token_id = int(logits.reshape(-1).argmax().item())
         self.position += 1
-        if self._cuda_available:
-            self.torch.cuda.synchronize()
         return logits
 
     def _decode_mask_independent(self) -> bool:
+        """Does the captured forward ignore ``attention_mask``?  True for the native step engine, and for the Python
+        forward when EVERY layer's attention is the patched decode kernel (no grouped-query heads): then the
+        per-step mask fill can be left out."""
         if self.engine == "step":
             return True
         from lemoq.kernels.attn_decode import _decode_forward_impl
 
         config = getattr(self.model, "config", None)
-        if getattr(config, "model_type", None) != "olmoe" or getattr(config, "output_attentions", False):
+        decoder_layers = getattr(getattr(self.model, "model", None), "layers", None) or ()
+        if getattr(config, "model_type", None) != "olmoe" or getattr(config, "output_attentions", False) or not decoder_layers:
             return False
-        layers = getattr(getattr(self.model, "model", None), "layers", ())
-        if not layers:
-            return False
-        for layer in layers:
-            attn = getattr(layer, "self_attn", None)
-            if (getattr(attn, "_lemoq_attn_backend", None) not in ("cuda", "triton")
-                    or getattr(getattr(attn, "forward", None), "__func__", None) is not _decode_forward_impl
-                    or getattr(attn, "num_key_value_groups", 1) != 1):
-                return False
-        return True
+
+        def kernel_attention(attn: Any) -> bool:
+            bound_to = getattr(getattr(attn, "forward", None), "__func__", None)
+            return (bound_to is _decode_forward_impl and getattr(attn, "_lemoq_attn_backend", None) in ("cuda", "triton")
+                    and getattr(attn, "num_key_value_groups", 1) == 1)
+
+        return all(kernel_attention(getattr(layer, "self_attn", None)) for layer in decoder_layers)
 
     def _set_step_inputs(self, *, skip_mask: bool = False) -> None:
+        """Write token, slot, position and length of the current step into the fixed buffers, and (unless skipped)
+        the additive mask that opens positions ``[0, position]``."""
         if skip_mask and not getattr(self, "_captured_mask_independent", False):
             raise RuntimeError("skip-mask-fill requires a captured mask-independent kernel backend")
-        if self.current_token_id is None:
-            raise RuntimeError("prefill must run before decode")
-        if self.position >= self.config.max_cache_len:
-            raise RuntimeError("decode position exceeded StaticCache capacity")
-        torch = self.torch
-        self.buffers.token.fill_(self.current_token_id)
-        self.buffers.cache_position.fill_(self.position)
-        self.buffers.position_ids.fill_(self.position)
+        token = self._seeded_token("decode")
+        self._room_for(1)
+        self.buffers.set_step(token=token, position=self.position)
         if not skip_mask:
-            self.buffers.attention_mask.fill_(torch.finfo(self.dtype).min)
-            self.buffers.attention_mask[..., : self.position + 1].zero_()
-        self.buffers.filled_len.fill_(self.position + 1)
+            mask = self.buffers.attention_mask
+            mask.fill_(self.torch.finfo(self.dtype).min)
+            mask[..., : self.position + 1] = 0
 
     def capture(self, *, warmup: int = 5) -> dict[str, Any]:
-        """Warm up eagerly on a side stream, restore the prefilled state, capture one forward."""
-        torch = self.torch
+        """Capture ONE decode forward on a stream of its own.  Before that: ``warmup`` eager steps on that stream (they
+        create every lazily built buffer), then a fresh prefill so the captured state is the prefilled one."""
         if self.graph is not None:
             return dict(self.capture_info)
         if warmup < 1:
             raise ValueError("warmup must be positive")
+        torch = self.torch
         try:
             self.prefill()
-            self.stream = torch.cuda.Stream(device=self.device)
-            self.stream.wait_stream(torch.cuda.current_stream(self.device))
-            initial_token, initial_position = self.current_token_id, self.position
-            with torch.cuda.stream(self.stream), torch.no_grad():
-                for _ in range(warmup):
+            seed = (self.current_token_id, self.position)
+            side = self.stream = torch.cuda.Stream(device=self.device)
+            main = torch.cuda.current_stream(self.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side), torch.no_grad():
+                for _ in range(warmup):  # same inputs every time: the steps only have to run, not to advance
                     self._set_step_inputs()
                     self._forward_once()
-            self.stream.synchronize()
+            side.synchronize()
             self.prefill()
-            self.current_token_id, self.position = initial_token, initial_position
-            self.stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(self.stream):
+            self.current_token_id, self.position = seed
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
                 self._set_step_inputs()
-            self.stream.synchronize()
+            side.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=self.stream), torch.no_grad():
+            with torch.cuda.graph(graph, stream=side), torch.no_grad():
                 self.logits = self._forward_once()
-            self.stream.synchronize()
-            self.graph = graph
-            self._captured_mask_independent = self._decode_mask_independent()
-            self.capture_info.update(mask_independent_decode=self._captured_mask_independent, capture_success=True,
-                                     stream="dedicated CUDA stream")
-            return dict(self.capture_info)
-        except Exception as exc:  # noqa: BLE001
+            side.synchronize()
+        except Exception as exc:  # noqa: BLE001 - every failure is reported with its stage
             raise CudaGraphCaptureError("capture", exc) from exc
+        self.graph = graph
+        self._captured_mask_independent = self._decode_mask_independent()
+        self.capture_info.update(capture_success=True, stream="dedicated CUDA stream",
+                                 mask_independent_decode=self._captured_mask_independent)
+        return dict(self.capture_info)
 
     def _replay_skip_mask(self) -> bool:
-        return _skip_mask_fill_enabled() and self._captured_mask_independent
+        return self._captured_mask_independent and _skip_mask_fill_enabled()
+
+    def _captured(self, purpose: str) -> None:
+        if self.graph is None or self.stream is None or self.logits is None:
+            raise RuntimeError("capture must succeed before %s" % purpose)
 
     def replay(self, *, synchronize: bool = True) -> Any:
-        """Replay one decode step; with ``synchronize`` also pick the next token and advance."""
-        if self.graph is None or self.stream is None or self.logits is None:
-            raise RuntimeError("capture must succeed before replay")
+        """One decode step through the graph.  With ``synchronize`` the host waits, adopts the pick and advances;
+        without, it only queues the step (same inputs next time)."""
+        self._captured("replay")
         try:
             with self.torch.cuda.stream(self.stream), self.torch.no_grad():
                 self._set_step_inputs(skip_mask=self._replay_skip_mask())
                 self.graph.replay()
             if synchronize:
                 self.stream.synchronize()
-                picked = self.step_next_token
-                # the native step engine picks the token itself (first maximal logit, like a host arg-max)
-                self.current_token_id = int(picked.item()) if picked is not None else int(self.logits.reshape(-1).argmax().item())
-                self.position += 1
-            self.capture_info["replay_success"] = True
-            return self.logits
+                self._adopt(self.logits)
         except Exception as exc:  # noqa: BLE001
             raise CudaGraphCaptureError("replay", exc) from exc
+        self.capture_info["replay_success"] = True
+        return self.logits
 
     def replay_chained(self, steps: int) -> list[int]:
         """``steps`` greedy decode steps with no host work in between (native step engine only): the step inputs go to
@@ -629,34 +643,30 @@ class StaticCacheDecodeSession:
             raise RuntimeError("replay_chained needs the captured native step engine")
         if steps <= 0:
             raise ValueError("steps must be positive")
-        if self.position + steps > self.config.max_cache_len:
-            raise RuntimeError("replay_chained: exceeded StaticCache capacity (%d + %d > %d)"
-                               % (self.position, steps, self.config.max_cache_len))
+        first_token = self._seeded_token("decode")
+        self._room_for(steps)
         torch = self.torch
         if self._chain_host is None or self._chain_host.numel() < steps + 4:
             self._chain_host = torch.zeros(max(steps, 64) + 4, dtype=torch.int64).pin_memory()
-        if self.current_token_id is None:
-            raise RuntimeError("prefill must run before decode")
+        scalars, tokens_out = self._chain_host[-4:], self._chain_host[:steps]
         try:
             with torch.cuda.stream(self.stream), torch.no_grad():
-                # the step scalars of the first step: one 32-byte copy from pinned host memory into the packed buffer
-                host_in = self.buffers.pack_step(self._chain_host[-4:], token=self.current_token_id, position=self.position)
-                self.buffers.packed.copy_(host_in, non_blocking=True)
+                # the first step's scalars: one 32-byte copy from pinned host memory into the packed buffer
+                self.buffers.packed.copy_(self.buffers.pack_step(scalars, token=first_token, position=self.position), non_blocking=True)
                 for _ in range(steps):
                     self.graph.replay()
-                log = self._step["token_log"][self.position: self.position + steps]
-                self._chain_host[:steps].copy_(log, non_blocking=True)
+                tokens_out.copy_(self._step["token_log"][self.position: self.position + steps], non_blocking=True)
             self.stream.synchronize()
         except Exception as exc:  # noqa: BLE001
             raise CudaGraphCaptureError("replay", exc) from exc
-        tokens = [int(v) for v in self._chain_host[:steps].tolist()]
+        tokens = [int(t) for t in tokens_out.tolist()]
         self.position += steps
         self.current_token_id = tokens[-1]
         return tokens
 
     def set_position(self, position: int) -> None:
-        if position < 0 or position >= self.config.max_cache_len:
-            raise RuntimeError("position %d 超出 StaticCache 容量 %d" % (position, self.config.max_cache_len))
+        if not 0 <= position < self.config.max_cache_len:
+            raise RuntimeError("position %d 超出 StaticCache 容量 %d (outside the cache)" % (position, self.config.max_cache_len))
         self.position = int(position)
 
     def replay_at_position(self, position: int, *, synchronize: bool = True) -> Any:
@@ -664,38 +674,36 @@ class StaticCacheDecodeSession:
         return self.replay(synchronize=synchronize)
 
     def time_graph_only(self, iters: int = 20) -> float:
-        """Mean device time (ms) of back-to-back graph replays at the current position, no host work
-        in between (CUDA events on the session stream)."""
-        torch = self.torch
+        """Mean device time (ms) of ``iters`` back-to-back replays with no host work between them, from CUDA events on
+        the session's stream.  The session's position is left as it was."""
         if self.graph is None:
             raise RuntimeError("capture must succeed before timing")
-        saved = self.position
-        if self._step is not None:  # the native step advances its own position: stay inside the cache
-            self.position = max(0, min(self.position, self.config.max_cache_len - iters - 4))
+        torch, here = self.torch, self.position
+        if self._step is not None:  # the native step advances its own position: start where iters + warm-up still fit
+            self.position = max(0, min(here, self.config.max_cache_len - iters - 4))
+        first, last = (torch.cuda.Event(enable_timing=True) for _ in range(2))
         with torch.cuda.stream(self.stream):
             self._set_step_inputs(skip_mask=self._replay_skip_mask())
-            self.position = saved
-            for _ in range(3):
+            self.position = here
+            for i in range(3 + iters):
+                if i == 3:
+                    first.record(self.stream)
                 self.graph.replay()
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record(self.stream)
-            for _ in range(iters):
-                self.graph.replay()
-            end.record(self.stream)
+            last.record(self.stream)
         self.stream.synchronize()
-        return start.elapsed_time(end) / iters
+        return first.elapsed_time(last) / iters
+
+    def _graph_output(self, value: Any) -> Any:
+        if self.stream is None or value is None:
+            raise RuntimeError("no graph output is available")
+        self.stream.synchronize()
+        return value
 
     def logits_cpu(self) -> Any:
-        if self.stream is None or self.logits is None:
-            raise RuntimeError("no graph output is available")
-        self.stream.synchronize()
-        return self.logits.detach().to("cpu").clone()
+        return self._graph_output(self.logits).detach().cpu().clone()
 
     def next_token_cpu(self) -> int:
-        if self.stream is None or self.current_token_id is None:
-            raise RuntimeError("no graph output is available")
-        self.stream.synchronize()
-        return self.current_token_id
+        return self._graph_output(self.current_token_id)
 
     def reset(self) -> None:
         self.prefill()

@@ -1,14 +1,22 @@
 // The whole decode step as ONE persistent cooperative kernel, built on 8-row weight tiles and the
 // int8 tensor-core dot product.
 //
-// One block per SM stays resident for the whole step; the phases of a layer are separated by a grid
-// barrier.  All weights move as TILES: 8 whole rows (+ the rows' group scales) brought into a
-// shared-memory stage by bulk asynchronous copies, one copy per row (rows land 64 bytes apart from
-// the natural stride, which keeps the 128-bit shared loads below free of bank conflicts).  Ten warps
-// of the block own one stage each and fill it IN THEIR OWN PROGRAM ORDER ACROSS PHASES, so while a
-// warp waits at a barrier the tiles of its next phases (q.k.v, KV cache, o_proj, router and lm_head
-// tiles do not depend on activations) are already landing; only the expert tiles have to wait for
-// the routing.
+// One block per SM stays resident for the whole step.  All weights move as TILES: 8 whole rows and the rows'
+// group scales, brought into a 16.6 KB shared-memory stage by two to four bulk asynchronous copies, each issued by
+// a lane of its own (the rows of a tile are adjacent in memory, so their codes are one run of bytes and their
+// scales another; an expert's 4 gate + 4 up rows, and a down tile that holds rows of two routed experts, are two
+// runs each).  The block has ten stages.  Ten CONSUMER warps own one stage
+// each and do all the arithmetic; five PRODUCER warps do nothing but issue copies: each keeps two stages filled,
+// walking the block's tile sequence of the WHOLE STEP in order (a copy instruction occupies the issuing warp for
+// well over a thousand cycles, which is why the consumers do not issue their own).  A stage is handed back and
+// forth through a full/empty pair of shared-memory barriers.  The producers run ahead across phases and layers:
+// q.k.v, KV-cache, o_proj, router and lm_head tiles do not depend on activations, so they land while the
+// consumers still work on the phase before; only the expert tiles wait, on the block's own top-k.
+//
+// Between phases the blocks exchange small vectors (the residual stream, q.k.v, router logits, the SwiGLU
+// activations) through global memory as flagged 8-byte words that the readers poll, see "flagged words" below.
+// The one place where every block needs everything every other block wrote in bulk - the attention partials
+// before o_proj - is a grid barrier: one per layer, plus one at the end of the step.
 //
 // Arithmetic: the activation vector of a phase is turned once per block into three planes of signed
 // 7-bit digits with one power-of-two scale per group of 128 (x = sx * (d2*2^14 + d1*2^7 + d0)).  The
@@ -27,14 +35,15 @@
 // partial sums in shared memory that the block adds in slot order.  No atomics on data: results are
 // bit-identical run to run.
 //
-// Phases per layer:
-//   A  q.k.v tiles          x = RMSNorm(x_prev) planes                          -> qkv, sum-of-squares partials
-//   B  attention            one (head, split) per block; KV tiles of 64 positions stream through the same
-//                           stages; fused q/k norm + RoPE + KV write            -> (m, l, acc) partial per unit
-//   C  o_proj tiles         the splits of each head are merged while the planes are built; + residual -> x1
-//   D  router tiles (fp16)  h2 = RMSNorm(x1) planes stay in shared memory for E   -> router logits
-//   E  expert gate/up       one warp per block derives the top-k; SwiGLU          -> act
-//   F  expert down          routing-weighted sum + residual                       -> x2
+// Phases per layer (what a block waits for -> what it publishes):
+//   A  q.k.v tiles          flagged x of the layer before; planes of RMSNorm(x)   -> flagged qkv + sum-of-squares partials
+//   B  attention            flagged qkv; one (head, split) per block, KV tiles of 64 positions through the same
+//                           stages; q/k norm + RoPE + KV row write fused          -> (m, l, acc) partial per unit
+//      grid barrier
+//   C  o_proj tiles         splits of each head merged while the planes are built; + residual -> flagged x1
+//   D  router tiles (fp16)  flagged x1; planes of h2 = RMSNorm(x1) stay in shared memory for E -> flagged logits
+//   E  expert gate/up       flagged logits; one warp per block derives the top-k; SwiGLU -> flagged act
+//   F  expert down          flagged act; routing-weighted sum + residual          -> flagged x2
 // then the lm_head tiles on RMSNorm(x2) as the q.k.v tiles of a pseudo layer, with the greedy pick.
 #include <algorithm>
 #include <cstddef>

@@ -1,40 +1,49 @@
-"""The seven decode-path switches: code defaults, ``LEMOQ_*`` environment overrides.
+"""The seven switches of the decode path (interface of the reference's src/lemoq/kernels/fusion_switches.py:40-76).
 
-Mirrors src/lemoq/kernels/fusion_switches.py:40-76 of the reference: an env value of
-``"1"`` turns a switch on, any other set value turns it off, unset means the default.
-Every default is True (the canonical cell).
+One table: switch name, environment variable, default.  The environment wins over the default: the value ``"1"``
+switches on, any other value that is set switches off.  Every default is on (the canonical cell).
 """
 
 from __future__ import annotations
 
 import os
-from typing import Any
-
-ENV_VARS: dict[str, str] = {
-    "fused_rope": "LEMOQ_FUSED_ROPE",
-    "fused_route": "LEMOQ_FUSED_ROUTE",
-    "skip_mask_fill": "LEMOQ_SKIP_MASK_FILL",
-    "packed_qkv": "LEMOQ_PACKED_QKV",
-    "kv_direct_write": "LEMOQ_KV_DIRECT_WRITE",
-    "lm_head_w8": "LEMOQ_LMHEAD_W8",
-    "kv_int8": "LEMOQ_KV_INT8",
-}
-
-FUSION_DEFAULTS: dict[str, bool] = {name: True for name in ENV_VARS}
+from typing import Any, Mapping, NamedTuple
 
 
-def fusion_enabled(name: str, env: dict[str, str] | None = None) -> bool:
-    """Effective state of one switch (env override first, then the code default)."""
-    if name not in ENV_VARS:
-        raise KeyError("未知融合开关 %r (unknown fusion switch); declared: %s" % (name, sorted(ENV_VARS)))
-    raw = (os.environ if env is None else env).get(ENV_VARS[name])
-    return FUSION_DEFAULTS[name] if raw is None else raw == "1"
+class _Switch(NamedTuple):
+    name: str
+    env: str
+    default: bool
 
 
-def fusion_states(env: dict[str, str] | None = None) -> dict[str, bool]:
-    return {name: fusion_enabled(name, env) for name in ENV_VARS}
+_TABLE = tuple(_Switch(name, "LEMOQ_" + suffix, True) for name, suffix in (
+    ("fused_rope", "FUSED_ROPE"),
+    ("fused_route", "FUSED_ROUTE"),
+    ("skip_mask_fill", "SKIP_MASK_FILL"),
+    ("packed_qkv", "PACKED_QKV"),
+    ("kv_direct_write", "KV_DIRECT_WRITE"),
+    ("lm_head_w8", "LMHEAD_W8"),
+    ("kv_int8", "KV_INT8"),
+))
+_BY_NAME = {s.name: s for s in _TABLE}
+
+ENV_VARS: dict[str, str] = {s.name: s.env for s in _TABLE}
+FUSION_DEFAULTS: dict[str, bool] = {s.name: s.default for s in _TABLE}
 
 
-def fusion_payload_fields(env: dict[str, str] | None = None) -> dict[str, Any]:
-    """One key per switch for a result's ``config`` block."""
-    return fusion_states(env)
+def fusion_enabled(name: str, env: Mapping[str, str] | None = None) -> bool:
+    """Is the switch on?  ``env`` replaces the process environment (tests)."""
+    switch = _BY_NAME.get(name)
+    if switch is None:
+        raise KeyError("未知融合开关 %r (unknown fusion switch); declared: %s" % (name, sorted(_BY_NAME)))
+    value = (os.environ if env is None else env).get(switch.env)
+    return FUSION_DEFAULTS[name] if value is None else value == "1"
+
+
+def fusion_states(env: Mapping[str, str] | None = None) -> dict[str, bool]:
+    return {s.name: fusion_enabled(s.name, env) for s in _TABLE}
+
+
+def fusion_payload_fields(env: Mapping[str, str] | None = None) -> dict[str, Any]:
+    """The switch states as fields of a result's ``config`` block."""
+    return dict(fusion_states(env))

@@ -62,26 +62,25 @@ def kv_int8_rows_applicable(k_new: Any, v_new: Any) -> bool:
 
 
 def kv_int8_bulk_quantize(cache_keys: Any, cache_values: Any, filled: Any = None) -> dict[str, Any]:
-    """Quantise a whole fp16 cache ``(1, H, S, D)``; slots at or beyond ``filled`` become code 0 /
-    scale 1 (``filled=None`` quantises every slot).  Returns ``kc/ks/vc/vs``."""
+    """Quantise a whole fp16 cache ``(1, H, S, D)`` into ``kc/ks/vc/vs``.  With ``filled`` in ``[1, S]`` only the
+    first ``filled`` slots are quantised and the rest become code 0 / scale 1.  ``filled=None`` quantises every
+    slot, and so does ``filled <= 0``: the reference's test is ``filled is not None and filled > 0``
+    (src/lemoq/kernels/kv_int8.py:147), so a zero length falls into its whole-cache branch."""
     _, h, s, d = (int(v) for v in cache_keys.shape)
     dev = cache_keys.device
     if filled is not None:
-        filled = int(filled.item()) if hasattr(filled, "item") else int(filled)
-        filled = max(0, min(filled, s))
+        filled = int(filled.item()) if hasattr(filled, "item") else int(filled)  # the init path may synchronise once
+    count = -1 if filled is None or filled <= 0 else min(filled, s)  # -1: every slot
     _cabi.require_cuda(cache_keys, cache_values, what="kv_int8_bulk_quantize")
-    keys = cache_keys.contiguous()
-    values = cache_values.contiguous()
-    if keys.dtype != torch.float16 or values.dtype != torch.float16:
+    if cache_keys.dtype != torch.float16 or cache_values.dtype != torch.float16:
         raise NotImplementedError("kv_int8_bulk_quantize: cache 只支持 fp16")
-    kc = torch.empty((1, h, s, d), dtype=torch.int8, device=dev)
-    vc = torch.empty((1, h, s, d), dtype=torch.int8, device=dev)
-    ks = torch.empty((1, h, s), dtype=torch.float16, device=dev)
-    vs = torch.empty((1, h, s), dtype=torch.float16, device=dev)
-    _cabi.call("lemoq_kv_int8_bulk_quantize", _cabi.ptr(keys), _cabi.ptr(values), _cabi.ptr(kc), _cabi.ptr(ks),
-               _cabi.ptr(vc), _cabi.ptr(vs), h, s, d, -1 if filled is None else int(filled),
-               _cabi.current_stream(dev))
-    return {"kc": kc, "ks": ks, "vc": vc, "vs": vs}
+    keys, values = cache_keys.contiguous(), cache_values.contiguous()
+    codes = lambda: torch.empty((1, h, s, d), dtype=torch.int8, device=dev)  # noqa: E731
+    scales = lambda: torch.empty((1, h, s), dtype=torch.float16, device=dev)  # noqa: E731
+    out = {"kc": codes(), "ks": scales(), "vc": codes(), "vs": scales()}
+    _cabi.call("lemoq_kv_int8_bulk_quantize", _cabi.ptr(keys), _cabi.ptr(values), _cabi.ptr(out["kc"]), _cabi.ptr(out["ks"]),
+               _cabi.ptr(out["vc"]), _cabi.ptr(out["vs"]), h, s, d, count, _cabi.current_stream(dev))
+    return out
 
 
 def kv_int8_init_buffers(layer_keys: Any, layer_values: Any, filled: Any = None) -> dict[str, Any]:

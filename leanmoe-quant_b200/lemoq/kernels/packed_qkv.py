@@ -1,6 +1,11 @@
-"""Packed q/k/v projection: one W8 GEMV over the concatenated ``[q; k; v]`` rows
-(reference: src/lemoq/kernels/packed_qkv.py).  Row-local reduction order, so the packed result is
-bit-identical to three separate calls."""
+"""Packed q/k/v projection: the three W8 projections of an attention module as ONE GEMV over their rows
+stacked ``[q; k; v]`` (the interface of the reference's src/lemoq/kernels/packed_qkv.py:50-164).
+
+The GEMV kernel reduces every output row on its own, in an order that does not depend on how many rows
+the call has, so the stacked call returns the very bits three separate calls return
+(tests/test_gpu_ops.py checks that).  The stacked buffers are built once, after quantisation and before
+any graph capture; the decode step hands their pointers to the native step engine.
+"""
 
 from __future__ import annotations
 
@@ -10,90 +15,104 @@ from typing import Any
 import torch
 
 SWITCH = "LEMOQ_PACKED_QKV"
+_ATTR = "_lemoq_packed_qkv"
+_ROLES = ("q_proj", "k_proj", "v_proj")
 
 
 def packed_qkv_enabled() -> bool:
+    """State of the ``packed_qkv`` fusion switch (read when the buffers are built)."""
     from lemoq.kernels.fusion_switches import fusion_enabled
 
     return fusion_enabled("packed_qkv")
 
 
 def packed_qkv_applicable(attn: Any, quantized: bool) -> bool:
-    """Both preconditions: ``attn == "kernel"`` and the cell is quantised; otherwise a no-op."""
-    return str(attn) == "kernel" and bool(quantized)
+    """The stacked projection exists only for the kernel attention on a quantised cell; everywhere else the
+    switch is a no-op (never a refusal)."""
+    return bool(quantized) and str(attn) == "kernel"
 
 
 def _attention_modules(model: Any) -> list[Any]:
-    from lemoq.kernels.attn_decode import _attention_modules as _select
+    from lemoq.kernels.attn_decode import _attention_modules as select
 
-    return list(_select(model))
+    return list(select(model))
+
+
+def _geometry(module: Any) -> tuple[int, int, int, int, int]:
+    return tuple(int(getattr(module, name)) for name in ("in_features", "out_features", "group_size", "padded_in", "n_groups"))
+
+
+def _check_projections(layer: Any, projections: dict[str, Any]) -> None:
+    """What the stacked form needs of each projection, one rule per line: (holds?, error type, message)."""
+    from lemoq.quant.linear import QuantLinear
+
+    for role, m in projections.items():
+        quantised = isinstance(m, QuantLinear)
+        rules = (
+            (quantised, ValueError, "packed q/k/v 需要已量化的 %s（layer=%r 得到 %s）" % (role, layer, type(m).__name__)),
+            (quantised and int(m.weight_bits) == 8, NotImplementedError,
+             "packed q/k/v 只支持 w8（%s 是 %s-bit）" % (role, getattr(m, "weight_bits", "?"))),
+            (quantised and bool(m.spec.symmetric) and m.zero is None, NotImplementedError, "packed q/k/v 只支持对称量化（%s）" % role),
+            (quantised and m.bias is None, NotImplementedError, "packed q/k/v 不支持带 bias 的投影（%s）" % role),
+        )
+        for holds, error, message in rules:
+            if not holds:
+                raise error(message)
+    shapes = sorted({_geometry(m) for m in projections.values()})
+    if len(shapes) > 1:
+        raise ValueError("packed q/k/v 要求三个投影的 (in, out, group, padded_in, n_groups) 完全一致，得到 %r" % (shapes,))
 
 
 @dataclass
 class PackedQKV:
+    """Stacked int8 codes ``(3 * out, in)`` and fp16 group scales ``(3 * out, in / group)`` of one attention module."""
+
     packed: Any
     scale: Any
     in_features: int
     out_features: int
     group_size: int
 
-    def project(self, x: Any) -> tuple[Any, Any, Any]:
-        from lemoq.kernels.dequant_gemv import dequant_gemm_fused
-
-        flat = x.reshape(-1, self.in_features)
-        if not flat.is_contiguous():
-            flat = flat.contiguous()
-        y = dequant_gemm_fused(flat, self.packed, self.scale, None, group_size=self.group_size, bits=8, symmetric=True,
-                               out_dtype=x.dtype)
-        y = y.reshape(*x.shape[:-1], 3, self.out_features)
-        return y[..., 0, :], y[..., 1, :], y[..., 2, :]
+    @classmethod
+    def stack(cls, q: Any, k: Any, v: Any) -> "PackedQKV":
+        parts = (q, k, v)
+        return cls(packed=torch.cat([m.packed for m in parts]).contiguous(), scale=torch.cat([m.scale for m in parts]).contiguous(),
+                   in_features=int(q.in_features), out_features=int(q.out_features), group_size=int(q.group_size))
 
     def combined(self, x: Any) -> Any:
-        return torch.cat(self.project(x), dim=-1)
+        """``[..., 3 * out]``: q, k and v of every row of ``x`` side by side (one kernel call)."""
+        from lemoq.kernels.dequant_gemv import dequant_gemm_fused
 
+        rows = x.reshape(-1, self.in_features).contiguous()
+        y = dequant_gemm_fused(rows, self.packed, self.scale, None, group_size=self.group_size, bits=8, symmetric=True,
+                               out_dtype=x.dtype)
+        return y.reshape(*x.shape[:-1], 3 * self.out_features)
 
-def _validate(layer: Any, q: Any, k: Any, v: Any) -> None:
-    from lemoq.quant.linear import QuantLinear
-
-    for role, module in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
-        if not isinstance(module, QuantLinear):
-            raise ValueError("packed q/k/v 需要已量化的 %s（layer=%r 得到 %s）" % (role, layer, type(module).__name__))
-        if int(module.weight_bits) != 8:
-            raise NotImplementedError("packed q/k/v 只支持 w8（%s 是 %d-bit）" % (role, int(module.weight_bits)))
-        if not bool(module.spec.symmetric) or module.zero is not None:
-            raise NotImplementedError("packed q/k/v 只支持对称量化（%s）" % role)
-        if module.bias is not None:
-            raise NotImplementedError("packed q/k/v 不支持带 bias 的投影（%s）" % role)
-    shape = {(int(m.in_features), int(m.out_features), int(m.group_size), int(m.padded_in), int(m.n_groups))
-             for m in (q, k, v)}
-    if len(shape) != 1:
-        raise ValueError("packed q/k/v 要求三个投影的 (in, out, group, padded_in, n_groups) 完全一致，得到 %r" % (sorted(shape),))
+    def project(self, x: Any) -> tuple[Any, Any, Any]:
+        """``(q, k, v)`` as views of the one result."""
+        q, k, v = self.combined(x).split(self.out_features, dim=-1)
+        return q, k, v
 
 
 def install_packed_qkv(model: Any) -> int:
-    """Build the concatenated buffers on every attention module (after quantisation, before capture)."""
-    installed = 0
-    for module in _attention_modules(model):
-        q, k, v = (getattr(module, n, None) for n in ("q_proj", "k_proj", "v_proj"))
-        _validate(getattr(module, "layer_idx", "?"), q, k, v)
-        module._lemoq_packed_qkv = PackedQKV(
-            packed=torch.cat((q.packed, k.packed, v.packed), dim=0).contiguous(),
-            scale=torch.cat((q.scale, k.scale, v.scale), dim=0).contiguous(),
-            in_features=int(q.in_features), out_features=int(q.out_features), group_size=int(q.group_size))
-        installed += 1
-    if not installed:
+    """Attach a :class:`PackedQKV` to every OLMoE attention module; returns how many.  Call it after quantisation and
+    before capture (it allocates)."""
+    modules = _attention_modules(model)
+    if not modules:
         raise RuntimeError("没有找到任何 OLMoE attention 模块 (no OLMoE attention module found)")
-    return installed
+    for module in modules:
+        projections = {role: getattr(module, role, None) for role in _ROLES}
+        _check_projections(getattr(module, "layer_idx", "?"), projections)
+        setattr(module, _ATTR, PackedQKV.stack(*projections.values()))
+    return len(modules)
 
 
 def packed_qkv_installed(model: Any) -> int:
-    return sum(1 for m in _attention_modules(model) if getattr(m, "_lemoq_packed_qkv", None) is not None)
+    return sum(getattr(m, _ATTR, None) is not None for m in _attention_modules(model))
 
 
 def remove_packed_qkv(model: Any) -> int:
-    removed = 0
-    for module in _attention_modules(model):
-        if getattr(module, "_lemoq_packed_qkv", None) is not None:
-            delattr(module, "_lemoq_packed_qkv")
-            removed += 1
-    return removed
+    carrying = [m for m in _attention_modules(model) if getattr(m, _ATTR, None) is not None]
+    for module in carrying:
+        delattr(module, _ATTR)
+    return len(carrying)

@@ -154,14 +154,16 @@ def kv_bulk_quantize(keys: torch.Tensor, values: torch.Tensor, filled: Optional[
 
     Follows src/lemoq/kernels/kv_int8.py:127-163: slots at or beyond ``filled``
     hold code 0 / scale 1; ``filled=None`` quantises every slot (a zero row also
-    yields code 0 / scale 1).
+    yields code 0 / scale 1).  ``filled <= 0`` takes the same branch as ``None``
+    there (the test is ``filled is not None and filled > 0``, :147), so it
+    quantises every slot too.
     """
     _, h, s, d = keys.shape
     out = {}
     for name, t in (("k", keys), ("v", values)):
         codes = torch.zeros((1, h, s, d), dtype=torch.int8)
         scales = torch.ones((1, h, s), dtype=torch.float16)
-        n = s if filled is None else max(0, min(int(filled), s))
+        n = s if filled is None or int(filled) <= 0 else min(int(filled), s)
         if n > 0:
             c, sc = kv_quantize_per_token(t[0, :, :n, :])
             codes[0, :, :n, :] = c

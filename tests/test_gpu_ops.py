@@ -150,7 +150,7 @@ def test_kv_int8_golden_bit_exact(ops_golden):
     kc, ks, vc, vs = kv_int8_write(row, row)
     assert torch.equal(kc.cpu(), T(g["kv_row_codes"], "cpu")) and torch.equal(ks.cpu(), T(g["kv_row_scale"], "cpu"))
     assert torch.equal(vc, kc) and torch.equal(vs, ks)
-    for tag, filled in (("full", None), ("part", 5)):
+    for tag, filled in (("full", None), ("part", 5), ("full", 0)):  # 0 behaves like None in the reference
         d = kv_int8_bulk_quantize(T(g["kv_cache_k"]), T(g["kv_cache_v"]), filled)
         for name in ("kc", "ks", "vc", "vs"):
             assert torch.equal(d[name].cpu(), T(g["kv_bulk_%s_%s" % (tag, name)], "cpu")), (tag, name)

@@ -46,7 +46,8 @@ def test_kv_quantisation_bit_exact(ops_golden):
     assert torch.equal(c, T(g["kv_row_codes"]))
     assert torch.equal(s, T(g["kv_row_scale"]))
     assert float(s[0, 2, 0]) == 1.0 and int(c[0, 2].abs().max()) == 0
-    for tag, filled in (("full", None), ("part", 5)):
+    # filled=0 takes the reference's whole-cache branch (its test is "filled is not None and filled > 0")
+    for tag, filled in (("full", None), ("part", 5), ("full", 0)):
         d = ops.kv_bulk_quantize(T(g["kv_cache_k"]), T(g["kv_cache_v"]), filled)
         for name in ("kc", "ks", "vc", "vs"):
             assert torch.equal(d[name], T(g["kv_bulk_%s_%s" % (tag, name)])), (tag, name)
