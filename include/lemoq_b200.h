@@ -86,12 +86,13 @@ LEMOQ_API int lemoq_dequant_gemv_w8(const void* x, int M, const int8_t* codes, c
                           int group_size, void* y, int out_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
- * W8 rows against many tokens (batched decode, tens of tokens per call): every
- * weight byte is read once per call whatever T is.  Two calls: the activations
- * are first turned into integer digit planes (lemoq_w8_quantise_tokens, planes of
- * lemoq_w8_token_planes_bytes(T, K) bytes, caller-provided), then
- * lemoq_w8_rows_tokens computes y[t, n] = fp16(sum_k x[t, k] * codes[e, n, k] *
- * scale[e, n, k/g]) with exact integer partial sums.
+ * W8 rows against many tokens (batched decode, prefill: tens of tokens per
+ * call): every weight byte is read once per block of 16 tokens.  Two calls: the
+ * activations are first turned into integer digit planes
+ * (lemoq_w8_quantise_tokens; planes of lemoq_w8_token_planes_bytes(T, K) bytes,
+ * caller-provided, layout private to the library), then lemoq_w8_rows_tokens
+ * computes y[t, n] = fp16(sum_k x[t, k] * codes[e, n, k] * scale[e, n, k/g]) with
+ * exact integer partial sums per group of 128 on the int8 tensor-core tile.
  * ref: the batched (T > 1) arms of the reference dequantise the weights and call
  *      a dense matmul: src/lemoq/quant/linear.py:365 (QuantLinear separate arm) and
  *      src/lemoq/kernels/moe_static.py:329 (_prefill_forward); same arithmetic,
@@ -100,7 +101,7 @@ LEMOQ_API int lemoq_dequant_gemv_w8(const void* x, int M, const int8_t* codes, c
  * array, tokens [seg[e], seg[e+1]) use expert e (tokens sorted by expert); NULL
  * with E == 1 means all T tokens.  gate_up != 0: N = 2F rows are gate [0, F) and up
  * [F, 2F); y is (T, F) = silu(gate) * up.  Otherwise y is (T, N).
- * K % 512 == 0, K <= 2048, N even, group_size % 16 == 0.
+ * K % 128 == 0, K <= 4096, N even, group_size % 128 == 0.
  */
 LEMOQ_API size_t lemoq_w8_token_planes_bytes(int T, int K);
 LEMOQ_API int lemoq_w8_quantise_tokens(const void* x, int T, int K, void* planes, void* stream);

@@ -236,7 +236,6 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--bandwidth-gbs", type=float, default=None)
     ap.add_argument("--dot-mode", type=int, default=None, help="lemoq_set_tuning key 0 (0 magic fp32, 1 exact cvt, 2 exact mixed)")
-    ap.add_argument("--debug", type=int, default=None, help="lemoq_set_tuning key 2 (timing experiments, wrong results)")
     ap.add_argument("--warm", action="store_true", help="no L2 flush between calls (data served from L2 when it fits)")
     ap.add_argument("--warps", type=int, default=None, help="lemoq_set_tuning key 1: warps per block of the streaming kernels")
     args = ap.parse_args()
@@ -249,8 +248,6 @@ def main() -> int:
         _cabi.call("lemoq_set_tuning", 0, args.dot_mode)
     if args.warps is not None:
         _cabi.call("lemoq_set_tuning", 1, args.warps)
-    if args.debug is not None:
-        _cabi.call("lemoq_set_tuning", 2, args.debug)
     print(json.dumps({"tuning": {"dot_mode": args.dot_mode, "warps": args.warps}}), flush=True)
     timer = Timer(args.iters)
     timer.warm = args.warm

@@ -1,19 +1,25 @@
-// W8 rows against MANY activation vectors (batched decode: tens of tokens per step).
+// W8 rows against MANY activation vectors (batched decode and prefill: tens of tokens per call).
 //
-// The batch-1 kernels stream every weight row once per token.  With T tokens in flight that would read
-// the weights T times; here a warp keeps its two weight rows in registers and walks all the tokens of its
-// segment, so every weight byte is read from memory once per call whatever T is (weights-stationary).
+// The batch-1 kernels stream every weight row once per token.  With T tokens in flight that would read the
+// weights T times; here a warp keeps a strip of 16 weight rows moving through its registers exactly once per
+// block of up to 16 tokens and meets all of them on the way (weights-stationary).
 //
-//   1. quantise_tokens_kernel   x (T, K) fp16 -> digit planes: per 16-element chunk a power-of-two scale sx
-//      and three planes of 7-bit digits, x = sx * (d2*2^14 + d1*2^7 + d0) (fp16 values within 2^9 of the
-//      chunk maximum are exact, the rest good to 2^-20 of it).  Done once per call, not once per block.
-//   2. w8_tokens_kernel         block = 8 warps x 2 rows; token tiles of 8 are staged in shared memory and
-//      shared by the block's warps; int8 codes meet the planes in dp4a (exact int32 partial sums), fp32
-//      combine and scale, fp16 result.  Segments: tokens [seg[e], seg[e+1]) use the weights of expert e
-//      (tokens sorted by expert), so a resident expert's rows are read once for all its tokens.
-//      Modes: plain rows (dense linears, expert down) and gate/up with the SwiGLU epilogue.
+//   1. quantise_tokens_kernel   x (T, K) fp16 -> three planes of 7-bit digits per token with one power-of-two
+//      scale per group of 128: x = sx * (d2*2^14 + d1*2^7 + d0).  fp16 values within 2^9 of the group maximum
+//      are exact, the rest good to 2^-20 of it.  Done once per call.
+//   2. w8_tokens_mma_kernel     one warp per strip of 16 rows (gate/up mode: 8 gate rows + their 8 up rows).
+//      The int8 weight codes are the A operand of mma.sync m16n8k32 s8 as they sit in memory; the B operand is
+//      TWO tokens: columns (token, plane) = (0,0) (0,1) (0,2) - (1,0) (1,1) (1,2) -.  The int32 sums of a
+//      128-group are exact; they are scaled by (row scale x token scale x plane weight) in fp32 and added up per
+//      column, and the three columns of a token are added at the very end.  The bytes a lane loads for A and B
+//      are the same permutation of k inside a 64-byte chunk, so 128-bit loads feed the fragments directly.
+//      Weights come straight from global memory into registers, requested three groups ahead and bypassing L1.
+//      All warps of a block work for the same expert, hence on the same tokens: the block stages the digit planes
+//      of eight tokens in shared memory (the loads from L1/L2 were the kernel's limit: warps stalled on them
+//      with the tensor pipe 5 % busy), every warp runs over its strip against them, then the next eight follow.
+//      Segments: tokens [seg[e], seg[e+1]) use the weights of expert e (tokens sorted by expert).
 //
-// HBM/L2-bound integer work on CUDA cores; no tensor cores.
+// HBM-bound for a few tokens per expert.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -21,38 +27,37 @@ namespace lemoq {
 
 namespace {
 
-constexpr int kTokTile = 8;     // tokens staged per tile
-constexpr int kRowWarps = 8;    // warps per block, two rows each
-constexpr int kMaxChunks = 4;   // K <= 2048
+constexpr int kStripWarps = 8;    // warps per block; a warp owns a strip of 16 rows, or a slice of k of one
+constexpr int kMaxPairs = 4;      // token pairs a warp carries through one pass over its strip
+constexpr int kAhead = 3;         // groups of 128 codes a warp keeps requested ahead
 
-// words of one quantised token: 3 planes x (K/16) lane chunks x 4 words, then K/16 chunk scales
-__host__ __device__ inline int plane_words(int K) { return 3 * (K / 16) * 4 + K / 16; }
+// bytes of one quantised token: 3 planes x K digits, then K/128 group scales (fp32)
+__host__ __device__ inline size_t token_plane_bytes(int K) { return static_cast<size_t>(3) * K + static_cast<size_t>(K / 128) * 4; }
 
-__device__ __forceinline__ void chunk_scale_pow2(float amax, float& sx, float& inv) {
-    const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
+__device__ __forceinline__ void group_scale_pow2(float amax, float& sx, float& inv) {
+    const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);  // biased exponent
     if (amax > 0.f && e > 20) {
         sx = __uint_as_float(static_cast<uint32_t>(e - 19) << 23);
         inv = __uint_as_float(static_cast<uint32_t>(254 - (e - 19)) << 23);
-    } else {
+    } else {  // zero or denormal-range group: a fixed tiny scale keeps the arithmetic exact
         sx = __uint_as_float(static_cast<uint32_t>(2) << 23);
         inv = __uint_as_float(static_cast<uint32_t>(252) << 23);
     }
 }
 
-// grid = T, block = K / 4 threads (four consecutive threads share a 16-element chunk)
-__global__ void quantise_tokens_kernel(const __half* __restrict__ x, int K, uint32_t* __restrict__ planes) {
+// grid = T, block = K / 4 threads: a warp owns one group of 128 values, a thread four of them
+__global__ void quantise_tokens_kernel(const __half* __restrict__ x, int K, uint8_t* __restrict__ planes) {
     const int t = blockIdx.x, item = threadIdx.x;
-    const int nlc = K / 16;
     const uint2 xv = *reinterpret_cast<const uint2*>(x + static_cast<int64_t>(t) * K + 4 * item);
     const __half* xh = reinterpret_cast<const __half*>(&xv);
     float f[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) f[j] = __half2float(xh[j]);
     float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float sx, inv;
-    chunk_scale_pow2(amax, sx, inv);
+    group_scale_pow2(amax, sx, inv);
     uint32_t X[4], Y[4], Z[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -60,16 +65,16 @@ __global__ void quantise_tokens_kernel(const __half* __restrict__ x, int K, uint
         Y[j] = X[j] >> 7;
         Z[j] = static_cast<uint32_t>(static_cast<int>(X[j]) >> 14);
     }
-    uint32_t* dst = planes + static_cast<int64_t>(t) * plane_words(K);
-    const int lc = item >> 2, w = item & 3;
-    dst[(0 * nlc + lc) * 4 + w] = __byte_perm(__byte_perm(X[0], X[1], 0x0040), __byte_perm(X[2], X[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
-    dst[(1 * nlc + lc) * 4 + w] = __byte_perm(__byte_perm(Y[0], Y[1], 0x0040), __byte_perm(Y[2], Y[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
-    dst[(2 * nlc + lc) * 4 + w] = __byte_perm(__byte_perm(Z[0], Z[1], 0x0040), __byte_perm(Z[2], Z[3], 0x0040), 0x5410);
-    if (w == 0) reinterpret_cast<float*>(dst + 3 * nlc * 4)[lc] = sx;
+    uint8_t* tok = planes + static_cast<size_t>(t) * token_plane_bytes(K);
+    uint32_t* d0 = reinterpret_cast<uint32_t*>(tok) + item;
+    d0[0] = __byte_perm(__byte_perm(X[0], X[1], 0x0040), __byte_perm(X[2], X[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    d0[K / 4] = __byte_perm(__byte_perm(Y[0], Y[1], 0x0040), __byte_perm(Y[2], Y[3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+    d0[K / 2] = __byte_perm(__byte_perm(Z[0], Z[1], 0x0040), __byte_perm(Z[2], Z[3], 0x0040), 0x5410);
+    if ((item & 31) == 0) reinterpret_cast<float*>(tok + static_cast<size_t>(3) * K)[item >> 5] = sx;
 }
 
 struct TokParams {
-    const uint32_t* planes;   // (T, plane_words(K))
+    const uint8_t* planes;    // (T, token_plane_bytes(K))
     const int8_t* codes;      // (E, N, K)
     const __half* scale;      // (E, N, K/group)
     const int32_t* seg;       // (E + 1) token offsets, or null: one segment [0, T)
@@ -77,134 +82,218 @@ struct TokParams {
     int T, N, K, group, E, gate_up;
 };
 
-// Sixteen per-lane partial sums -> sixteen warp totals with 16 shuffles: every round halves the values a
-// lane carries and doubles the lanes that agree.  Afterwards lane L holds the total of value
-// ((L>>4)&1)*8 + ((L>>3)&1)*4 + ((L>>2)&1)*2 + ((L>>1)&1) (both lanes of an even/odd pair hold the same).
-__device__ __forceinline__ float warp_reduce16(float (&v)[16], int lane) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const bool up = (lane & 16) != 0;
-        const float keep = up ? v[i + 8] : v[i], give = up ? v[i] : v[i + 8];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const bool up = (lane & 8) != 0;
-        const float keep = up ? v[i + 4] : v[i], give = up ? v[i] : v[i + 4];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const bool up = (lane & 4) != 0;
-        const float keep = up ? v[i + 2] : v[i], give = up ? v[i] : v[i + 2];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, 4);
-    }
-    {
-        const bool up = (lane & 2) != 0;
-        const float keep = up ? v[1] : v[0], give = up ? v[0] : v[1];
-        v[0] = keep + __shfl_xor_sync(0xffffffffu, give, 2);
-    }
-    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// grid = (ceil(row pairs / kRowWarps), E); dynamic smem = kTokTile * plane_words(K) * 4 bytes.
-// One row pair per warp: its weights stay in registers while the warp walks all token tiles of the segment.
-// (A variant that kept the token tile and walked eight row pairs per warp was slower for the experts: the
-// serial weight loads of a warp are not hidden, thousands of small blocks hide them better.)
-template <int NCH>
-__global__ void __launch_bounds__(kRowWarps * 32) w8_tokens_kernel(const TokParams p) {
-    extern __shared__ __align__(16) uint32_t tile[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int e = blockIdx.y;
-    const int t0 = p.seg ? p.seg[e] : 0, t1 = p.seg ? p.seg[e + 1] : p.T;
-    if (t1 <= t0) return;
-    const int pairs = p.N / 2;
-    const int nlc = p.K / 16, gK = p.K / p.group, pw = plane_words(p.K);
-    const int64_t base = static_cast<int64_t>(e) * p.N;
-    uint4 w[2][NCH];
-    float sc[2][NCH];
-    auto load_rows = [&](int pair) {
-        // rows of the pair: (2i, 2i+1), or (n, N/2 + n) when the gate and the up row meet in the SwiGLU epilogue
-        const int r0 = p.gate_up ? pair : 2 * pair, r1 = p.gate_up ? pairs + pair : 2 * pair + 1;
+// The codes of one group of 128 of the warp's two rows per lane (rows g and g + 8 of the strip), and the rows'
+// group scales.  A lane holds bytes [16q, 16q + 16) of each 64-byte chunk, q = lane & 3.
+struct GroupRegs {
+    uint4 lo[2], hi[2];  // [chunk of 64]: row g, row g + 8
+    float ws_lo, ws_hi;
+};
+
+// What a lane knows about its strip and its columns.
+struct Lane {
+    const int8_t* w_lo;      // codes of row g of the strip, at byte 16q
+    const int8_t* w_hi;      // codes of row g + 8
+    const __half* s_lo;      // group scales of the two rows
+    const __half* s_hi;
+    uint32_t b_smem;         // shared address of this lane's plane row of token col_tok of pair 0, at byte 16q
+    uint32_t sx_smem;        // shared address of the group scales of token res_tok of pair 0
+    uint32_t pair_stride;    // bytes between the plane rows of consecutive pairs (two tokens)
+    uint32_t sx_pair_stride;
+    int group;               // weight group size
+    int col_tok;             // token of the pair whose (token, plane) column this lane feeds to B
+    bool col_on;             // false: padding column
+    float pw0, pw1;          // plane weights of the lane's two result columns
+};
+
+__device__ __forceinline__ void load_group(const Lane& L, GroupRegs& r, int grp) {
+    const int k0 = grp << 7;
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-            const int lc = c * 32 + lane;
-            const bool on = pair < pairs && lc < nlc;
+    for (int c = 0; c < 2; ++c) {
+        r.lo[c] = ld_stream16(L.w_lo + k0 + 64 * c);
+        r.hi[c] = ld_stream16(L.w_hi + k0 + 64 * c);
+    }
+    const int sg = k0 / L.group;
+    r.ws_lo = __half2float(__ldg(L.s_lo + sg));
+    r.ws_hi = __half2float(__ldg(L.s_hi + sg));
+}
+
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// One pass of a warp over groups [g0, g1) of its strip against the npairs token pairs staged in shared memory
+// (ntok tokens; the second token of the last pair may be missing).  Pairs are taken two at a time: their
+// loads, two independent chains of four MMAs, their fp32 updates.
+__device__ __forceinline__ void strip_pass(const Lane& L, int g0, int g1, int npairs, int ntok, float (&acc)[kMaxPairs][4]) {
+    GroupRegs ring[kAhead];
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int64_t row = base + (r == 0 ? r0 : r1);
-                w[r][c] = on ? ld_stream16(p.codes + row * p.K + lc * 16) : make_uint4(0, 0, 0, 0);
-                sc[r][c] = on ? __half2float(p.scale[row * gK + (lc * 16) / p.group]) : 0.f;
+    for (int i = 0; i < kAhead; ++i)
+        if (g0 + i < g1) load_group(L, ring[i], g0 + i);
+    for (int grp0 = g0; grp0 < g1; grp0 += kAhead) {
+#pragma unroll
+        for (int i = 0; i < kAhead; ++i) {
+            const int grp = grp0 + i;
+            if (grp < g1) {
+                const uint32_t koff = static_cast<uint32_t>(grp) << 7;
+                const float f_lo0 = ring[i].ws_lo * L.pw0, f_lo1 = ring[i].ws_lo * L.pw1;
+                const float f_hi0 = ring[i].ws_hi * L.pw0, f_hi1 = ring[i].ws_hi * L.pw1;
+#pragma unroll
+                for (int pb = 0; pb < kMaxPairs; pb += 2) {
+                    if (pb < npairs) {  // warp-uniform
+                        uint4 b[2][2];
+                        float sx[2];
+                        int c4[2][4];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const bool on = L.col_on && 2 * (pb + u) + L.col_tok < ntok;
+#pragma unroll
+                            for (int c = 0; c < 2; ++c)
+                                b[u][c] = on ? lds_u128(L.b_smem + (pb + u) * L.pair_stride + koff + 64 * c) : make_uint4(0, 0, 0, 0);
+                            sx[u] = pb + u < npairs ? lds_f32(L.sx_smem + (pb + u) * L.sx_pair_stride + 4 * grp) : 0.f;
+                            c4[u][0] = c4[u][1] = c4[u][2] = c4[u][3] = 0;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) mma_s8(c4[u], ring[i].lo[c].x, ring[i].hi[c].x, ring[i].lo[c].y, ring[i].hi[c].y, b[u][c].x, b[u][c].y);
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) mma_s8(c4[u], ring[i].lo[c].z, ring[i].hi[c].z, ring[i].lo[c].w, ring[i].hi[c].w, b[u][c].z, b[u][c].w);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            acc[pb + u][0] = fmaf(static_cast<float>(c4[u][0]), f_lo0 * sx[u], acc[pb + u][0]);
+                            acc[pb + u][1] = fmaf(static_cast<float>(c4[u][1]), f_lo1 * sx[u], acc[pb + u][1]);
+                            acc[pb + u][2] = fmaf(static_cast<float>(c4[u][2]), f_hi0 * sx[u], acc[pb + u][2]);
+                            acc[pb + u][3] = fmaf(static_cast<float>(c4[u][3]), f_hi1 * sx[u], acc[pb + u][3]);
+                        }
+                    }
+                }
+                if (grp + kAhead < g1) load_group(L, ring[i], grp + kAhead);  // the slot is free again
             }
         }
-    };
-    auto stage_tile = [&](int tb, int nt) {
-        __syncthreads();  // the previous tile has been consumed
-        const uint4* src = reinterpret_cast<const uint4*>(p.planes + static_cast<int64_t>(tb) * pw);
-        uint4* dst = reinterpret_cast<uint4*>(tile);
-        for (int i = threadIdx.x; i < nt * pw / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+}
+
+// Shared memory of a block: the digit planes of up to 2 * kMaxPairs tokens, rows [token][plane] of K + 64 bytes (the
+// 64 bytes keep the 128-bit loads of a quarter warp on different banks), then the tokens' group scales.
+__host__ __device__ inline size_t stage_row_bytes(int K) { return static_cast<size_t>(K) + 64; }
+__host__ __device__ inline size_t stage_bytes(int K) {
+    return static_cast<size_t>(2 * kMaxPairs) * 3 * stage_row_bytes(K) + static_cast<size_t>(2 * kMaxPairs) * (K / 128) * 4 +
+           static_cast<size_t>(kStripWarps) * kMaxPairs * 4 * 32 * 4;
+}
+
+// grid = (ceil(strips * kslices / kStripWarps), E), block = kStripWarps warps.  All warps of a block work for the same
+// expert, hence on the same tokens: the block stages the planes of 2 * kMaxPairs tokens in shared memory, every
+// warp runs over its strip (or its slice of k) against them, and the next tokens follow.  With kslices > 1 the
+// warps of a block split the k range of a strip and add their sums through shared memory in slice order (few
+// strips, dense linears: more requests in flight per strip).
+__global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(const TokParams p, const int kslices) {
+    extern __shared__ __align__(16) uint8_t stage[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int e = blockIdx.y;
+    const int t0 = p.seg ? p.seg[e] : 0, t1 = p.seg ? p.seg[e + 1] : p.T;
+    if (t1 <= t0) return;  // the whole block: every warp of a block has the same expert
+    const int half_rows = p.N / 2;
+    const int strips = p.gate_up ? (half_rows + 7) / 8 : (p.N + 15) / 16;
+    const int per_block = kStripWarps / kslices;
+    const int slice = warp / per_block;
+    const int strip = blockIdx.x * per_block + (warp - slice * per_block);
+    const bool live = strip < strips;
+    // the two rows of this lane; rows beyond the end are read as the last row and never stored
+    const int out_lo = p.gate_up ? strip * 8 + g : strip * 16 + g;        // gate row n       | row
+    const int out_hi = p.gate_up ? out_lo : out_lo + 8;                   // (same n)         | row + 8
+    const int lim = p.gate_up ? half_rows : p.N;
+    const int row_lo = max(0, min(out_lo, lim - 1)), row_hi = p.gate_up ? half_rows + row_lo : max(0, min(out_hi, lim - 1));
+    const int ngroups = p.K >> 7, gK = p.K / p.group;
+    const int64_t base = static_cast<int64_t>(e) * p.N;
+    const uint32_t row_bytes = static_cast<uint32_t>(stage_row_bytes(p.K));
+    const uint32_t stage_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
+    float* sx_stage = reinterpret_cast<float*>(stage + static_cast<size_t>(2 * kMaxPairs) * 3 * row_bytes);
+    float* red = sx_stage + 2 * kMaxPairs * ngroups;  // [warp][kMaxPairs * 4][32]
+    Lane L;
+    L.w_lo = p.codes + (base + row_lo) * p.K + 16 * q;
+    L.w_hi = p.codes + (base + row_hi) * p.K + 16 * q;
+    L.s_lo = p.scale + (base + row_lo) * gK;
+    L.s_hi = p.scale + (base + row_hi) * gK;
+    // B operand: column lane >> 2 = (token (lane >> 4) of the pair, plane (lane >> 2) & 3); plane 3 is padding
+    L.col_tok = lane >> 4;
+    L.col_on = (g & 3) < 3;
+    L.b_smem = stage_u32 + (static_cast<uint32_t>(L.col_tok) * 3 + static_cast<uint32_t>(min(g & 3, 2))) * row_bytes + 16 * q;
+    L.pair_stride = 6 * row_bytes;
+    // result columns 2q and 2q + 1: token q >> 1 of the pair, planes 2 * (q & 1) and 2 * (q & 1) + 1
+    L.sx_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sx_stage)) + static_cast<uint32_t>(q >> 1) * ngroups * 4;
+    L.sx_pair_stride = 2 * ngroups * 4;
+    L.group = p.group;
+    L.pw0 = (q & 1) ? 16384.f : 1.f;
+    L.pw1 = (q & 1) ? 0.f : 128.f;
+    const int gper = ngroups / kslices, g0 = slice * gper, g1 = g0 + gper;
+    const size_t tok_bytes = token_plane_bytes(p.K);
+    const int units = p.K >> 4;  // 16-byte units of a plane row
+
+    for (int tb = t0; tb < t1; tb += 2 * kMaxPairs) {
+        const int ntok = min(2 * kMaxPairs, t1 - tb), npairs = (ntok + 1) >> 1;  // block-uniform
+        __syncthreads();  // the previous tokens have been consumed
+        for (int u = threadIdx.x; u < ntok * 3 * units; u += blockDim.x) {
+            const int r = u / units, c = u - r * units, t = r / 3;  // r = token * 3 + plane
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.planes + static_cast<size_t>(tb + t) * tok_bytes + static_cast<size_t>(r - 3 * t) * p.K) + c);
+            *reinterpret_cast<uint4*>(stage + static_cast<size_t>(r) * row_bytes + 16 * c) = v;
+        }
+        for (int u = threadIdx.x; u < ntok * ngroups; u += blockDim.x) {
+            const int t = u / ngroups;
+            sx_stage[u] = __ldg(reinterpret_cast<const float*>(p.planes + static_cast<size_t>(tb + t) * tok_bytes + static_cast<size_t>(3) * p.K) + (u - t * ngroups));
+        }
         __syncthreads();
-    };
-    auto compute_tile = [&](int pair, int tb, int nt) {
-        float acc[16];  // [token][row]
+        float acc[kMaxPairs][4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+        for (int i = 0; i < kMaxPairs; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        if (live) strip_pass(L, g0, g1, npairs, ntok, acc);
+        if (kslices > 1) {  // slices 1.. hand their sums to slice 0, which adds them in slice order
+            if (slice > 0) {
 #pragma unroll
-        for (int tt = 0; tt < kTokTile; ++tt) {
-            if (tt < nt) {
-                const uint32_t* xq = tile + tt * pw;
-                const float* sxs = reinterpret_cast<const float*>(xq + 3 * nlc * 4);
+                for (int i = 0; i < kMaxPairs * 4; ++i) red[(warp * kMaxPairs * 4 + i) * 32 + lane] = acc[i >> 2][i & 3];
+            }
+            __syncthreads();
+            if (slice == 0) {
+                for (int s2 = 1; s2 < kslices; ++s2) {
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    const int lc = c * 32 + lane;
-                    if (lc < nlc) {
-                        const uint4 x0 = *reinterpret_cast<const uint4*>(xq + (0 * nlc + lc) * 4);
-                        const uint4 x1 = *reinterpret_cast<const uint4*>(xq + (1 * nlc + lc) * 4);
-                        const uint4 x2 = *reinterpret_cast<const uint4*>(xq + (2 * nlc + lc) * 4);
-                        const float sx = sxs[lc];
+                    for (int i = 0; i < kMaxPairs * 4; ++i) acc[i >> 2][i & 3] += red[((warp + s2 * per_block) * kMaxPairs * 4 + i) * 32 + lane];
+                }
+            }
+        }
+        if (!live || slice != 0) continue;
+        // planes of a token: two columns in this lane, the third (and the padding) in the lane next to it
 #pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            const uint4 ww = w[r][c];
-                            int s0 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x0.x), 0);
-                            int s1 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x1.x), 0);
-                            int s2 = __dp4a(static_cast<int>(ww.x), static_cast<int>(x2.x), 0);
-                            s0 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x0.y), s0);
-                            s1 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x1.y), s1);
-                            s2 = __dp4a(static_cast<int>(ww.y), static_cast<int>(x2.y), s2);
-                            s0 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x0.z), s0);
-                            s1 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x1.z), s1);
-                            s2 = __dp4a(static_cast<int>(ww.z), static_cast<int>(x2.z), s2);
-                            s0 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x0.w), s0);
-                            s1 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x1.w), s1);
-                            s2 = __dp4a(static_cast<int>(ww.w), static_cast<int>(x2.w), s2);
-                            const float tsum = fmaf(static_cast<float>(s2), 16384.f, fmaf(static_cast<float>(s1), 128.f, static_cast<float>(s0)));
-                            acc[2 * tt + r] = fmaf(tsum, sx * sc[r][c], acc[2 * tt + r]);
-                        }
+        for (int pr = 0; pr < kMaxPairs; ++pr) {
+            if (pr < npairs) {  // warp-uniform
+                float v_lo = acc[pr][0] + acc[pr][1], v_hi = acc[pr][2] + acc[pr][3];
+                v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+                v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+                const int tok = tb + 2 * pr + (q >> 1);
+                if ((q & 1) == 0 && tok < t1) {
+                    if (p.gate_up) {
+                        if (out_lo < half_rows)
+                            p.y[static_cast<int64_t>(tok) * half_rows + out_lo] = __float2half_rn(v_lo * (1.0f / (1.0f + expf(-v_lo))) * v_hi);
+                    } else {
+                        if (out_lo < p.N) p.y[static_cast<int64_t>(tok) * p.N + out_lo] = __float2half_rn(v_lo);
+                        if (out_hi < p.N) p.y[static_cast<int64_t>(tok) * p.N + out_hi] = __float2half_rn(v_hi);
                     }
                 }
             }
         }
-        const float total = warp_reduce16(acc, lane);
-        // this lane's value: token tt, row r
-        const int idx = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-        const int tt = idx >> 1, r = idx & 1;
-        // gate (r = 0) and up (r = 1) of one token sit in lanes that differ in bit 1 (every lane takes part)
-        const float other = __shfl_xor_sync(0xffffffffu, total, 2);
-        if (pair < pairs && tt < nt && (lane & 1) == 0) {
-            const int64_t tok = tb + tt;
-            if (p.gate_up) {
-                if (r == 0) p.y[tok * pairs + pair] = __float2half_rn(total * (1.0f / (1.0f + expf(-total))) * other);
-            } else {
-                p.y[tok * p.N + (r == 0 ? 2 * pair : 2 * pair + 1)] = __float2half_rn(total);
-            }
-        }
-    };
-    const int pair = blockIdx.x * kRowWarps + warp;
-    load_rows(pair);
-    for (int tb = t0; tb < t1; tb += kTokTile) {
-        const int nt = min(kTokTile, t1 - tb);
-        stage_tile(tb, nt);
-        compute_tile(pair, tb, nt);
     }
 }
 
@@ -214,59 +303,57 @@ __global__ void __launch_bounds__(kRowWarps * 32) w8_tokens_kernel(const TokPara
 using namespace lemoq;
 
 extern "C" size_t lemoq_w8_token_planes_bytes(int T, int K) {
-    if (T <= 0 || K <= 0 || K % 16 != 0) return 0;
-    return static_cast<size_t>(T) * plane_words(K) * sizeof(uint32_t);
+    if (T <= 0 || K <= 0 || K % 128 != 0) return 0;
+    return static_cast<size_t>(T) * token_plane_bytes(K);
 }
 
 extern "C" int lemoq_w8_quantise_tokens(const void* x, int T, int K, void* planes, void* stream) {
     LEMOQ_REQUIRE(T >= 0 && K > 0, LEMOQ_ERR_INVALID, "w8_quantise_tokens: bad shape");
-    LEMOQ_REQUIRE(K % 128 == 0 && K <= 2048 * 2, LEMOQ_ERR_UNSUPPORTED, "w8_quantise_tokens: K=%d must be a multiple of 128, <= 4096", K);
+    LEMOQ_REQUIRE(K % 128 == 0 && K <= 4096, LEMOQ_ERR_UNSUPPORTED, "w8_quantise_tokens: K=%d must be a multiple of 128, <= 4096", K);
     if (T == 0) return LEMOQ_OK;
     LEMOQ_REQUIRE(x && planes && aligned16(x) && aligned16(planes), LEMOQ_ERR_INVALID, "w8_quantise_tokens: null or unaligned pointer");
     LaunchCfg lc;
     lc.stream = static_cast<cudaStream_t>(stream);
     return launch_kernel(quantise_tokens_kernel, dim3(T), dim3(K / 4), 0, lc, reinterpret_cast<const __half*>(x), K,
-                         reinterpret_cast<uint32_t*>(planes));
+                         reinterpret_cast<uint8_t*>(planes));
 }
 
 extern "C" int lemoq_w8_rows_tokens(const void* planes, int T, const int8_t* codes, const void* scale, int N, int K, int group_size,
                                     const int32_t* seg_offsets, int E, int gate_up, void* y, void* stream) {
     LEMOQ_REQUIRE(T >= 0 && N > 0 && K > 0 && E >= 1, LEMOQ_ERR_INVALID, "w8_rows_tokens: bad shape");
     LEMOQ_REQUIRE(N % 2 == 0, LEMOQ_ERR_UNSUPPORTED, "w8_rows_tokens: N=%d must be even", N);
-    LEMOQ_REQUIRE(K % 512 == 0 && K <= 512 * kMaxChunks, LEMOQ_ERR_UNSUPPORTED, "w8_rows_tokens: K=%d must be a multiple of 512, <= 2048", K);
-    LEMOQ_REQUIRE(group_size > 0 && group_size % 16 == 0 && K % group_size == 0, LEMOQ_ERR_INVALID, "w8_rows_tokens: bad group_size %d", group_size);
+    LEMOQ_REQUIRE(K % 128 == 0 && K <= 4096, LEMOQ_ERR_UNSUPPORTED, "w8_rows_tokens: K=%d must be a multiple of 128, <= 4096", K);
+    LEMOQ_REQUIRE(group_size > 0 && K % group_size == 0, LEMOQ_ERR_INVALID, "w8_rows_tokens: bad group_size %d", group_size);
+    LEMOQ_REQUIRE(group_size % 128 == 0, LEMOQ_ERR_UNSUPPORTED, "w8_rows_tokens: group_size=%d must be a multiple of 128", group_size);
     LEMOQ_REQUIRE(E == 1 || seg_offsets, LEMOQ_ERR_INVALID, "w8_rows_tokens: several experts need segment offsets");
     if (T == 0) return LEMOQ_OK;
     LEMOQ_REQUIRE(planes && codes && scale && y && aligned16(planes) && aligned16(codes), LEMOQ_ERR_INVALID,
                   "w8_rows_tokens: null or unaligned pointer");
     TokParams p;
-    p.planes = reinterpret_cast<const uint32_t*>(planes);
+    p.planes = reinterpret_cast<const uint8_t*>(planes);
     p.codes = codes;
     p.scale = reinterpret_cast<const __half*>(scale);
     p.seg = seg_offsets;
     p.y = reinterpret_cast<__half*>(y);
     p.T = T; p.N = N; p.K = K; p.group = group_size; p.E = E; p.gate_up = gate_up ? 1 : 0;
-    const int pairs = N / 2;
-    dim3 grid((pairs + kRowWarps - 1) / kRowWarps, E), block(kRowWarps * 32);
-    const size_t smem = static_cast<size_t>(kTokTile) * plane_words(K) * sizeof(uint32_t);
+    const int strips = gate_up ? (N / 2 + 7) / 8 : (N + 15) / 16;
+    // a dense linear with few strips: split the k range of a strip over 2 or 4 warps so that the machine has enough
+    // requests in flight (148 SMs x 16 resident warps)
+    int kslices = 1;
+    const int ngroups = K / 128;
+    if (E == 1) {
+        if (strips * 2 <= 148 * 16 && ngroups % 4 == 0) kslices = 4;
+        else if (strips <= 148 * 16 && ngroups % 2 == 0) kslices = 2;
+    }
+    const int per_block = kStripWarps / kslices;
+    dim3 grid((strips + per_block - 1) / per_block, E), block(kStripWarps * 32);
+    const size_t smem = stage_bytes(K);
+    {  // per device and idempotent; not a stream operation, so legal under capture
+        const cudaError_t err = cudaFuncSetAttribute(w8_tokens_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(stage_bytes(4096)));
+        if (err != cudaSuccess) return set_error(LEMOQ_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(err));
+    }
     LaunchCfg lc;
     lc.stream = static_cast<cudaStream_t>(stream);
-    const int nch = K / 512;
-#define LEMOQ_TOK_CASE(NCHV)                                                                                          \
-    case NCHV: {                                                                                                      \
-        if (smem > 48 * 1024) {                                                                                       \
-            const cudaError_t err = cudaFuncSetAttribute(w8_tokens_kernel<NCHV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (err != cudaSuccess) return set_error(LEMOQ_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(err)); \
-        }                                                                                                             \
-        return launch_kernel(w8_tokens_kernel<NCHV>, grid, block, smem, lc, p);                                       \
-    }
-    switch (nch) {
-        LEMOQ_TOK_CASE(1)
-        LEMOQ_TOK_CASE(2)
-        LEMOQ_TOK_CASE(3)
-        LEMOQ_TOK_CASE(4)
-        default: break;
-    }
-#undef LEMOQ_TOK_CASE
-    return set_error(LEMOQ_ERR_UNSUPPORTED, "w8_rows_tokens: K=%d", K);
+    return launch_kernel(w8_tokens_mma_kernel, grid, block, smem, lc, p, kslices);
 }

@@ -39,7 +39,8 @@ def test_grouped_experts_sorted_pairs():
     gu_c, gu_s = ops.rtn_quantize_w8(gu, 128)
     dn_c, dn_s = ops.rtn_quantize_w8(dn, 128)
     q = ops.QuantExperts(gu_c, gu_s, dn_c, dn_s, 128)
-    ids = torch.tensor([0, 0, 0, 1, 3, 3, 3, 3, 3, 3, 3, 3, 3, 4], dtype=torch.int64)  # expert 2 has no pair; 3 spans tiles
+    # expert 2 has no pair; expert 3 has more pairs than a warp carries through one pass over its rows (16), and an odd count
+    ids = torch.tensor([0, 0, 0, 1] + [3] * 37 + [4], dtype=torch.int64)
     x = torch.randn(ids.numel(), hidden, generator=g).half()
     got = w8_experts_tokens(x.to(DEV), ids.to(DEV), gu_c.to(DEV), gu_s.to(DEV), dn_c.to(DEV), dn_s.to(DEV), group_size=128)
     one = torch.ones(1, dtype=torch.float16)
