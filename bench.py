@@ -59,12 +59,13 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "source": "fallback (6.65 TB/s, earlier measurement on this pool)"}
 
 
-def workload_config(ctx: int, layers: int, world: int, bytes_per_step: int) -> dict:
-    """The ``config`` block both arms print: the workload, nothing about how an arm runs it."""
+def workload_config(ctx: int, layers: int, world: int, bytes_first_step: int) -> dict:
+    """The ``config`` block both arms print: the workload, nothing about how an arm runs it (``bytes_first_step``: the
+    byte model at the first decoded position, so that the text does not depend on how many steps an arm times)."""
     return {"workload": "OLMoE-1B-7B architecture batch-1 greedy decode, W8A16 g128 + lm_head W8 + INT8 KV, "
                         "ctx %d, one decoded token per step (benchmark configuration 2)" % ctx,
             "ctx": ctx, "layers": layers,
-            "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (bytes_per_step / 1e9),
+            "l2": "inputs larger than L2: %.2f GB streamed per step vs 126 MB L2" % (bytes_first_step / 1e9),
             "parallelism": "replicas only" if world > 1 else "single GPU"}
 
 
@@ -201,12 +202,12 @@ def run_reference(args) -> int:
     from lemoq.model import OlmoeConfig
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    budget = byte_budget(ModelSpec.from_config(OlmoeConfig()), args.ctx + max(3, args.warmup) + steps // 2 + 1, CANONICAL_QUANT, kv_int8=True)
+    first = byte_budget(ModelSpec.from_config(OlmoeConfig()), args.ctx + 1, CANONICAL_QUANT, kv_int8=True)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": workload_config(args.ctx, spec.layers, world, budget["T"]),
+        "config": workload_config(args.ctx, spec.layers, world, first["T"]),
         "run": {"weights": "synthetic int8 codes and fp16 scales of the canonical shapes (the work of a step does not depend on the values)",
                 "threads": torch.get_num_threads()},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
@@ -220,8 +221,9 @@ def run_reference(args) -> int:
 # GPU arm
 # ----------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum of one step_tile_kernel launch, from one ncu capture of
-# `python bench.py --steps 4 --warmup 3 --no-cpu-baseline` (summary under profiles/): (ctx, layers) -> bytes.
-WHOLE_STEP_DRAM_TRAFFIC = {(1024, 16): 1268504320 + 5156608}
+# `python bench.py --steps 4 --warmup 3 --no-cpu-baseline --no-sub-records` (summary under profiles/):
+# (ctx, layers) -> bytes.
+WHOLE_STEP_DRAM_TRAFFIC = {(1024, 16): 1269527296 + 4218624}
 
 
 def time_dominant_kernel(model, peaks, iters: int = 20) -> dict:
@@ -492,7 +494,7 @@ def run_gpu(args) -> int:
         "metric": METRIC, "value": world * 1000.0 / dev_ms, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
-        "config": workload_config(ctx, model.config.num_hidden_layers, world, budget["T"]),
+        "config": workload_config(ctx, model.config.num_hidden_layers, world, byte_budget(spec, ctx + 1, CANONICAL_QUANT, kv_int8=True)["T"]),
         "run": {"engine": session.capture_info.get("engine"), "step_kernel": session.capture_info.get("step_kernel"),
                 "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0, RTN-quantised on the GPU",
                 "execution": "one CUDA graph per step"},

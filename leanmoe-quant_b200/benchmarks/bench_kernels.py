@@ -117,27 +117,28 @@ def bench_moe(timer: Timer, tokens_list, peak: float) -> None:
                distinct_experts=distinct, note="bytes count each distinct expert once")
         if t > 1:
             # the many-token form: pairs sorted by expert, weights-stationary kernels (each distinct expert read once)
-            from lemoq.kernels.batched_w8 import w8_experts_tokens
+            from lemoq.kernels.batched_w8 import expert_segments, w8_experts_tokens
 
             def sorted_pairs():
                 flat = state["ids"].reshape(-1)
                 order = torch.argsort(flat, stable=True)
                 state["pair_x"] = x[torch.div(order, k, rounding_mode="floor")].contiguous()
                 state["pair_e"] = flat[order].contiguous()
+                state["seg"] = expert_segments(state["pair_e"], e)
 
             def setup_pairs(i):
                 setup(i)
                 sorted_pairs()
 
             def many():
-                w8_experts_tokens(state["pair_x"], state["pair_e"], gu_c, gu_s, dn_c, dn_s, group_size=128)
+                w8_experts_tokens(state["pair_x"], state["pair_e"], gu_c, gu_s, dn_c, dn_s, group_size=128, seg_offsets=state["seg"])
 
             setup_pairs(0)
             distinct = int(torch.unique(state["ids"]).numel())
             us = timer.cold(many, setup_pairs)
             report("moe_w8 many-token kernels (quantise + gate_up + quantise + down, pairs sorted by expert)",
                    distinct * per_expert_w8 + t * h * 2 * 2, us, timer.floor_us, peak, tokens=t, distinct_experts=distinct,
-                   note="bytes count each distinct expert once; the sort and the routing-weighted combine are outside")
+                   note="bytes count each distinct expert once; the sort, the segment offsets and the routing-weighted combine are outside")
         if t == 1:
             us = timer.cold(gate_up, setup)
             report("moe_gate_up_w8", k * (2 * f * h + 2 * f * (h // 128) * 2) + h * 2 + k * f * 2, us, timer.floor_us, peak, tokens=t)

@@ -366,7 +366,7 @@ class ExpertParallelDecoder:
         def linear(xin, codes, scale, gs):
             # many tokens: the weights-stationary kernel; shapes it does not take go through the per-token GEMV
             k = int(codes.shape[1])
-            if k % 512 == 0 and k <= 2048 and int(codes.shape[0]) % 2 == 0:
+            if k % 128 == 0 and k <= 4096 and gs % 128 == 0 and int(codes.shape[0]) % 2 == 0:
                 return w8_linear_tokens(xin, codes, scale, group_size=gs)
             return dequant_gemm_fused(xin, codes, scale, group_size=gs, out_dtype=torch.float16)
         from lemoq.kernels.routing import routing_softmax_topk

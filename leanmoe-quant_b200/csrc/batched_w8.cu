@@ -20,6 +20,8 @@
 //      Segments: tokens [seg[e], seg[e+1]) use the weights of expert e (tokens sorted by expert).
 //
 // HBM-bound for a few tokens per expert.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -27,12 +29,15 @@ namespace lemoq {
 
 namespace {
 
-constexpr int kStripWarps = 8;    // warps per block; a warp owns a strip of 16 rows, or a slice of k of one
+constexpr int kStripWarps = 8;    // warps per block; a warp owns a strip of 16 rows
 constexpr int kMaxPairs = 4;      // token pairs a warp carries through one pass over its strip
 constexpr int kAhead = 3;         // groups of 128 codes a warp keeps requested ahead
 
-// bytes of one quantised token: 3 planes x K digits, then K/128 group scales (fp32)
-__host__ __device__ inline size_t token_plane_bytes(int K) { return static_cast<size_t>(3) * K + static_cast<size_t>(K / 128) * 4; }
+// bytes of one quantised token: 3 planes x K digits, then K/128 group scales (fp32), rounded up to 16 so that every
+// token starts on a 16-byte boundary (the planes are moved with 16-byte copies; K = 128 and 256 need the padding)
+__host__ __device__ inline size_t token_plane_bytes(int K) {
+    return (static_cast<size_t>(3) * K + static_cast<size_t>(K / 128) * 4 + 15) & ~static_cast<size_t>(15);
+}
 
 __device__ __forceinline__ void group_scale_pow2(float amax, float& sx, float& inv) {
     const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);  // biased exponent
@@ -102,6 +107,7 @@ struct Lane {
     const __half* s_lo;      // group scales of the two rows
     const __half* s_hi;
     uint32_t b_smem;         // shared address of this lane's plane row of token col_tok of pair 0, at byte 16q
+    uint32_t b_zero;         // shared address of the row of zeros, at byte 16q
     uint32_t sx_smem;        // shared address of the group scales of token res_tok of pair 0
     uint32_t pair_stride;    // bytes between the plane rows of consecutive pairs (two tokens)
     uint32_t sx_pair_stride;
@@ -134,19 +140,27 @@ __device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
     return v;
 }
 
-// One pass of a warp over groups [g0, g1) of its strip against the npairs token pairs staged in shared memory
-// (ntok tokens; the second token of the last pair may be missing).  Pairs are taken two at a time: their
-// loads, two independent chains of four MMAs, their fp32 updates.
-__device__ __forceinline__ void strip_pass(const Lane& L, int g0, int g1, int npairs, int ntok, float (&acc)[kMaxPairs][4]) {
-    GroupRegs ring[kAhead];
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// One pass of a warp over the ngroups groups of its strip against the npairs token pairs staged in shared memory
+// (ntok tokens; the second token of the last pair may be missing).  `ring` holds the first kAhead groups already.
+// Pairs are taken two at a time: their loads, two independent chains of four MMAs, their fp32 updates.
+__device__ __forceinline__ void strip_pass(const Lane& L, GroupRegs (&ring)[kAhead], int ngroups, int npairs, int ntok,
+                                           float (&acc)[kMaxPairs][4]) {
+    uint32_t b_addr[kMaxPairs], sx_addr[kMaxPairs];
 #pragma unroll
-    for (int i = 0; i < kAhead; ++i)
-        if (g0 + i < g1) load_group(L, ring[i], g0 + i);
-    for (int grp0 = g0; grp0 < g1; grp0 += kAhead) {
+    for (int pr = 0; pr < kMaxPairs; ++pr) {  // the padding column and a missing token read the row of zeros
+        b_addr[pr] = L.col_on && 2 * pr + L.col_tok < ntok ? L.b_smem + pr * L.pair_stride : L.b_zero;
+        sx_addr[pr] = L.sx_smem + pr * L.sx_pair_stride;
+    }
+    for (int grp0 = 0; grp0 < ngroups; grp0 += kAhead) {
 #pragma unroll
         for (int i = 0; i < kAhead; ++i) {
             const int grp = grp0 + i;
-            if (grp < g1) {
+            if (grp < ngroups) {
                 const uint32_t koff = static_cast<uint32_t>(grp) << 7;
                 const float f_lo0 = ring[i].ws_lo * L.pw0, f_lo1 = ring[i].ws_lo * L.pw1;
                 const float f_hi0 = ring[i].ws_hi * L.pw0, f_hi1 = ring[i].ws_hi * L.pw1;
@@ -158,11 +172,9 @@ __device__ __forceinline__ void strip_pass(const Lane& L, int g0, int g1, int np
                         int c4[2][4];
 #pragma unroll
                         for (int u = 0; u < 2; ++u) {
-                            const bool on = L.col_on && 2 * (pb + u) + L.col_tok < ntok;
 #pragma unroll
-                            for (int c = 0; c < 2; ++c)
-                                b[u][c] = on ? lds_u128(L.b_smem + (pb + u) * L.pair_stride + koff + 64 * c) : make_uint4(0, 0, 0, 0);
-                            sx[u] = pb + u < npairs ? lds_f32(L.sx_smem + (pb + u) * L.sx_pair_stride + 4 * grp) : 0.f;
+                            for (int c = 0; c < 2; ++c) b[u][c] = lds_u128(b_addr[pb + u] + koff + 64 * c);
+                            sx[u] = lds_f32(sx_addr[pb + u] + 4 * grp);
                             c4[u][0] = c4[u][1] = c4[u][2] = c4[u][3] = 0;
                         }
 #pragma unroll
@@ -181,37 +193,39 @@ __device__ __forceinline__ void strip_pass(const Lane& L, int g0, int g1, int np
                         }
                     }
                 }
-                if (grp + kAhead < g1) load_group(L, ring[i], grp + kAhead);  // the slot is free again
+                if (grp + kAhead < ngroups) load_group(L, ring[i], grp + kAhead);  // the slot is free again
             }
         }
     }
 }
 
 // Shared memory of a block: the digit planes of up to 2 * kMaxPairs tokens, rows [token][plane] of K + 64 bytes (the
-// 64 bytes keep the 128-bit loads of a quarter warp on different banks), then the tokens' group scales.
+// 64 bytes keep the 128-bit loads of a quarter warp on different banks), one row of zeros (what the padding column and a
+// missing token read), then the tokens' group scales.
 __host__ __device__ inline size_t stage_row_bytes(int K) { return static_cast<size_t>(K) + 64; }
 __host__ __device__ inline size_t stage_bytes(int K) {
-    return static_cast<size_t>(2 * kMaxPairs) * 3 * stage_row_bytes(K) + static_cast<size_t>(2 * kMaxPairs) * (K / 128) * 4 +
-           static_cast<size_t>(kStripWarps) * kMaxPairs * 4 * 32 * 4;
+    return static_cast<size_t>(2 * kMaxPairs * 3 + 1) * stage_row_bytes(K) + static_cast<size_t>(2 * kMaxPairs) * (K / 128) * 4;
 }
 
-// grid = (ceil(strips * kslices / kStripWarps), E), block = kStripWarps warps.  All warps of a block work for the same
-// expert, hence on the same tokens: the block stages the planes of 2 * kMaxPairs tokens in shared memory, every
-// warp runs over its strip (or its slice of k) against them, and the next tokens follow.  With kslices > 1 the
-// warps of a block split the k range of a strip and add their sums through shared memory in slice order (few
-// strips, dense linears: more requests in flight per strip).
-__global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(const TokParams p, const int kslices) {
+// grid = (token chunks, ceil(strips / kStripWarps), E), block = kStripWarps warps.  All warps of a block work for the
+// same expert, hence on the same tokens: the block stages the planes of 2 * kMaxPairs tokens in shared memory, every
+// warp runs over its strip against them, and the next tokens follow.  tok_chunk > 0 (dense linears with few rows)
+// gives each block only tok_chunk of the tokens, so that more warps stream at the same time; the blocks that
+// share rows are neighbours in the grid and meet in L2.
+__global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(const TokParams p, const int tok_chunk) {
     extern __shared__ __align__(16) uint8_t stage[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, q = lane & 3;
-    const int e = blockIdx.y;
-    const int t0 = p.seg ? p.seg[e] : 0, t1 = p.seg ? p.seg[e + 1] : p.T;
-    if (t1 <= t0) return;  // the whole block: every warp of a block has the same expert
+    const int e = blockIdx.z;
+    int t0 = p.seg ? p.seg[e] : 0, t1 = p.seg ? p.seg[e + 1] : p.T;
+    if (tok_chunk > 0) {
+        t0 += static_cast<int>(blockIdx.x) * tok_chunk;
+        t1 = min(t1, t0 + tok_chunk);
+    }
+    if (t1 <= t0) return;  // the whole block: every warp of a block has the same tokens
     const int half_rows = p.N / 2;
     const int strips = p.gate_up ? (half_rows + 7) / 8 : (p.N + 15) / 16;
-    const int per_block = kStripWarps / kslices;
-    const int slice = warp / per_block;
-    const int strip = blockIdx.x * per_block + (warp - slice * per_block);
+    const int strip = blockIdx.y * kStripWarps + warp;
     const bool live = strip < strips;
     // the two rows of this lane; rows beyond the end are read as the last row and never stored
     const int out_lo = p.gate_up ? strip * 8 + g : strip * 16 + g;        // gate row n       | row
@@ -222,8 +236,9 @@ __global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(cons
     const int64_t base = static_cast<int64_t>(e) * p.N;
     const uint32_t row_bytes = static_cast<uint32_t>(stage_row_bytes(p.K));
     const uint32_t stage_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
-    float* sx_stage = reinterpret_cast<float*>(stage + static_cast<size_t>(2 * kMaxPairs) * 3 * row_bytes);
-    float* red = sx_stage + 2 * kMaxPairs * ngroups;  // [warp][kMaxPairs * 4][32]
+    const uint32_t zero_row = stage_u32 + static_cast<uint32_t>(2 * kMaxPairs * 3) * row_bytes;
+    float* sx_stage = reinterpret_cast<float*>(stage + static_cast<size_t>(2 * kMaxPairs * 3 + 1) * row_bytes);
+    for (uint32_t u = threadIdx.x * 16; u < row_bytes; u += blockDim.x * 16) *reinterpret_cast<uint4*>(stage + static_cast<size_t>(2 * kMaxPairs * 3) * row_bytes + u) = make_uint4(0, 0, 0, 0);
     Lane L;
     L.w_lo = p.codes + (base + row_lo) * p.K + 16 * q;
     L.w_hi = p.codes + (base + row_hi) * p.K + 16 * q;
@@ -233,6 +248,7 @@ __global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(cons
     L.col_tok = lane >> 4;
     L.col_on = (g & 3) < 3;
     L.b_smem = stage_u32 + (static_cast<uint32_t>(L.col_tok) * 3 + static_cast<uint32_t>(min(g & 3, 2))) * row_bytes + 16 * q;
+    L.b_zero = zero_row + 64 + 16 * q;  // + 64: other banks than the plane row the neighbouring lanes read
     L.pair_stride = 6 * row_bytes;
     // result columns 2q and 2q + 1: token q >> 1 of the pair, planes 2 * (q & 1) and 2 * (q & 1) + 1
     L.sx_smem = static_cast<uint32_t>(__cvta_generic_to_shared(sx_stage)) + static_cast<uint32_t>(q >> 1) * ngroups * 4;
@@ -240,41 +256,37 @@ __global__ void __launch_bounds__(kStripWarps * 32, 2) w8_tokens_mma_kernel(cons
     L.group = p.group;
     L.pw0 = (q & 1) ? 16384.f : 1.f;
     L.pw1 = (q & 1) ? 0.f : 128.f;
-    const int gper = ngroups / kslices, g0 = slice * gper, g1 = g0 + gper;
     const size_t tok_bytes = token_plane_bytes(p.K);
     const int units = p.K >> 4;  // 16-byte units of a plane row
 
+    GroupRegs ring[kAhead];
     for (int tb = t0; tb < t1; tb += 2 * kMaxPairs) {
         const int ntok = min(2 * kMaxPairs, t1 - tb), npairs = (ntok + 1) >> 1;  // block-uniform
+        // the first groups of the strip are requested before the tokens are staged: both latencies overlap
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < kAhead; ++i)
+                if (i < ngroups) load_group(L, ring[i], i);
+        }
         __syncthreads();  // the previous tokens have been consumed
         for (int u = threadIdx.x; u < ntok * 3 * units; u += blockDim.x) {
             const int r = u / units, c = u - r * units, t = r / 3;  // r = token * 3 + plane
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.planes + static_cast<size_t>(tb + t) * tok_bytes + static_cast<size_t>(r - 3 * t) * p.K) + c);
-            *reinterpret_cast<uint4*>(stage + static_cast<size_t>(r) * row_bytes + 16 * c) = v;
+            cp_async16(stage_u32 + static_cast<uint32_t>(r) * row_bytes + 16 * c,
+                       p.planes + static_cast<size_t>(tb + t) * tok_bytes + static_cast<size_t>(r - 3 * t) * p.K + 16 * c);
         }
         for (int u = threadIdx.x; u < ntok * ngroups; u += blockDim.x) {
             const int t = u / ngroups;
             sx_stage[u] = __ldg(reinterpret_cast<const float*>(p.planes + static_cast<size_t>(tb + t) * tok_bytes + static_cast<size_t>(3) * p.K) + (u - t * ngroups));
         }
+        // a missing second token of the last pair: its scales are read (and multiplied by zero sums)
+        if ((ntok & 1) && threadIdx.x < ngroups) sx_stage[ntok * ngroups + threadIdx.x] = 0.f;
+        cp_async_wait_all();
         __syncthreads();
+        if (!live) continue;  // took part in the staging only
         float acc[kMaxPairs][4];
 #pragma unroll
         for (int i = 0; i < kMaxPairs; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-        if (live) strip_pass(L, g0, g1, npairs, ntok, acc);
-        if (kslices > 1) {  // slices 1.. hand their sums to slice 0, which adds them in slice order
-            if (slice > 0) {
-#pragma unroll
-                for (int i = 0; i < kMaxPairs * 4; ++i) red[(warp * kMaxPairs * 4 + i) * 32 + lane] = acc[i >> 2][i & 3];
-            }
-            __syncthreads();
-            if (slice == 0) {
-                for (int s2 = 1; s2 < kslices; ++s2) {
-#pragma unroll
-                    for (int i = 0; i < kMaxPairs * 4; ++i) acc[i >> 2][i & 3] += red[((warp + s2 * per_block) * kMaxPairs * 4 + i) * 32 + lane];
-                }
-            }
-        }
-        if (!live || slice != 0) continue;
+        strip_pass(L, ring, ngroups, npairs, ntok, acc);
         // planes of a token: two columns in this lane, the third (and the padding) in the lane next to it
 #pragma unroll
         for (int pr = 0; pr < kMaxPairs; ++pr) {
@@ -337,16 +349,16 @@ extern "C" int lemoq_w8_rows_tokens(const void* planes, int T, const int8_t* cod
     p.y = reinterpret_cast<__half*>(y);
     p.T = T; p.N = N; p.K = K; p.group = group_size; p.E = E; p.gate_up = gate_up ? 1 : 0;
     const int strips = gate_up ? (N / 2 + 7) / 8 : (N + 15) / 16;
-    // a dense linear with few strips: split the k range of a strip over 2 or 4 warps so that the machine has enough
-    // requests in flight (148 SMs x 16 resident warps)
-    int kslices = 1;
-    const int ngroups = K / 128;
+    // a dense linear with few strips: give every block only a part of the tokens, so that the machine has enough
+    // warps streaming (148 SMs x 8 and more); with experts the tokens of a block are its expert's segment
+    int tok_chunk = 0, chunks = 1;
     if (E == 1) {
-        if (strips * 2 <= 148 * 16 && ngroups % 4 == 0) kslices = 4;
-        else if (strips <= 148 * 16 && ngroups % 2 == 0) kslices = 2;
+        const int want = (148 * 8 + strips - 1) / strips;                   // blocks wanted per strip
+        chunks = std::min(std::max(want, (T + 2 * kMaxPairs - 1) / (2 * kMaxPairs)), (T + 1) / 2);  // and one pass per block
+        tok_chunk = ((T + chunks - 1) / chunks + 1) & ~1;                 // even: tokens travel in pairs
+        chunks = (T + tok_chunk - 1) / tok_chunk;
     }
-    const int per_block = kStripWarps / kslices;
-    dim3 grid((strips + per_block - 1) / per_block, E), block(kStripWarps * 32);
+    dim3 grid(chunks, (strips + kStripWarps - 1) / kStripWarps, E), block(kStripWarps * 32);
     const size_t smem = stage_bytes(K);
     {  // per device and idempotent; not a stream operation, so legal under capture
         const cudaError_t err = cudaFuncSetAttribute(w8_tokens_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -355,5 +367,5 @@ extern "C" int lemoq_w8_rows_tokens(const void* planes, int T, const int8_t* cod
     }
     LaunchCfg lc;
     lc.stream = static_cast<cudaStream_t>(stream);
-    return launch_kernel(w8_tokens_mma_kernel, grid, block, smem, lc, p, kslices);
+    return launch_kernel(w8_tokens_mma_kernel, grid, block, smem, lc, p, tok_chunk);
 }

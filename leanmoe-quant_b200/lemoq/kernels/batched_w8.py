@@ -1,5 +1,5 @@
-"""W8 linears and grouped experts for MANY tokens per call (batched decode): weights-stationary kernels,
-every weight byte read once per call.  The reference's T > 1 arms dequantise and call a dense matmul
+"""W8 linears and grouped experts for MANY tokens per call (batched decode): weights-stationary kernels on the int8
+tensor-core tile, every weight byte read once per block of tokens.  The reference's T > 1 arms dequantise and call a dense matmul
 (`quant/linear.py:365`, `moe_static.py:329`); these compute the same sums with exact integer partial sums.
 CUDA only: there is no CPU path."""
 
@@ -47,17 +47,23 @@ def w8_linear_tokens(x: Any, codes: Any, scale: Any, *, group_size: int) -> Any:
     return w8_rows_tokens(quantise_tokens(x.contiguous()), int(x.shape[0]), codes, scale, group_size=group_size)
 
 
-def w8_experts_tokens(x: Any, expert_ids: Any, gate_up: Any, gate_up_scale: Any, down: Any, down_scale: Any, *,
-                      group_size: int) -> Any:
-    """Grouped experts on pairs SORTED by expert: ``x (R, H)`` fp16, ``expert_ids (R,)`` ascending local ids ->
-    ``(R, H)`` fp16 unweighted expert outputs (gate/up + SwiGLU, then down).  Rows whose id is >= the number of
-    experts (padding of a static-capacity exchange) must come last; their outputs are left unwritten."""
-    r = int(x.shape[0])
-    e = int(gate_up.shape[0])
-    # counts without a data-dependent shape (no host sync: usable under stream capture); ids >= e (padding rows
-    # sorted behind the real ones) belong to no segment and are never touched
-    counts = (expert_ids.reshape(-1, 1) == torch.arange(e, device=x.device).reshape(1, -1)).sum(dim=0)
-    seg = torch.zeros(e + 1, dtype=torch.int32, device=x.device)
+def expert_segments(expert_ids: Any, experts: int) -> Any:
+    """``(experts + 1,)`` int32 offsets of the segments of ``expert_ids`` (ascending local ids): rows ``[seg[e], seg[e+1])``
+    belong to expert e.  No data-dependent shape and no host read: usable under stream capture.  Ids ``>= experts``
+    (padding rows of a static-capacity exchange, sorted behind the real ones) belong to no segment."""
+    counts = (expert_ids.reshape(-1, 1) == torch.arange(experts, device=expert_ids.device).reshape(1, -1)).sum(dim=0)
+    seg = torch.zeros(experts + 1, dtype=torch.int32, device=expert_ids.device)
     seg[1:] = torch.cumsum(counts, dim=0).to(torch.int32)
-    act = w8_rows_tokens(quantise_tokens(x.contiguous()), r, gate_up, gate_up_scale, group_size=group_size, seg_offsets=seg, gate_up=True)
-    return w8_rows_tokens(quantise_tokens(act), r, down, down_scale, group_size=group_size, seg_offsets=seg)
+    return seg
+
+
+def w8_experts_tokens(x: Any, expert_ids: Any, gate_up: Any, gate_up_scale: Any, down: Any, down_scale: Any, *,
+                      group_size: int, seg_offsets: Any = None) -> Any:
+    """Grouped experts on rows SORTED by expert: ``x (R, H)`` fp16, ``expert_ids (R,)`` ascending local ids ->
+    ``(R, H)`` fp16 unweighted expert outputs (gate/up + SwiGLU, then down).  Rows whose id is >= the number of
+    experts must come last; their outputs are left unwritten.  ``seg_offsets`` (from :func:`expert_segments`) may be
+    handed in by a caller that already has it."""
+    rows = int(x.shape[0])
+    seg = expert_segments(expert_ids, int(gate_up.shape[0])) if seg_offsets is None else seg_offsets
+    act = w8_rows_tokens(quantise_tokens(x.contiguous()), rows, gate_up, gate_up_scale, group_size=group_size, seg_offsets=seg, gate_up=True)
+    return w8_rows_tokens(quantise_tokens(act), rows, down, down_scale, group_size=group_size, seg_offsets=seg)

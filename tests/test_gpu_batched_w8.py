@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("tokens,n,k", [(13, 96, 2048), (1, 64, 512), (64, 258, 1024)])
+# K = 128 and 256: a token's planes and scales are not a multiple of 16 bytes by themselves
+@pytest.mark.parametrize("tokens,n,k", [(13, 96, 2048), (1, 64, 512), (64, 258, 1024), (5, 64, 256), (3, 32, 128)])
 def test_dense_rows_many_tokens(tokens, n, k):
     from lemoq.kernels.batched_w8 import w8_linear_tokens
 
