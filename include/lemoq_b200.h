@@ -109,6 +109,32 @@ LEMOQ_API int lemoq_w8_rows_tokens(const void* planes, int T, const int8_t* code
                          int group_size, const int32_t* seg_offsets, int E, int gate_up, void* y, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Row bookkeeping of the expert-parallel exchange (batched decode over several
+ * GPUs, benchmark configuration 5).  These have no counterpart in the reference
+ * (it has no multi-GPU code).  The contract: expert e lives on rank e / (experts / world),
+ * rows travel sorted by (expert id, pair index), every peer gets a fixed block of
+ * P = T * K row slots, a row is H fp16 activations + 8 fp16 of which the first is
+ * the expert id, unused slots carry the id `experts`.  All arrays are device
+ * memory; nothing is read on the host (legal under stream capture).
+ *   lemoq_ep_dispatch: h (T, H) fp16, top_i (T, K) int64 -> send (world, P, H + 8) fp16,
+ *       slot (P) int32 = send slot of pair (t, k), src (world * P) int32 scratch.
+ *   lemoq_ep_regroup:  recv (R = world * P, H + 8) fp16 as received -> x_sorted (R, H)
+ *       fp16 rows in local-expert order (zeros behind the real rows), perm (R) int32,
+ *       seg (experts / world + 1) int32 segment offsets for lemoq_w8_rows_tokens.
+ *   lemoq_ep_return:   y_sorted (R, H) -> y (R, H) in slot order (rows of unused slots untouched).
+ *   lemoq_ep_combine:  back (world * P, H) fp16, slot, top_w (T, K) fp16 -> out (T, H) fp16,
+ *       out[t] = sum_k top_w[t, k] * back[slot[t * K + k]] in slot order, fp32.
+ * T * K <= 4096, R <= 4096, experts <= 2048, H % 8 == 0.  err_flag (may be NULL):
+ * LEMOQ_FLAG_BAD_EXPERT for an id outside its range (clamped / treated as padding).
+ */
+LEMOQ_API int lemoq_ep_dispatch(const void* h, const int64_t* top_i, int T, int K, int H, int experts, int world, void* send,
+                      int32_t* slot, int32_t* src, int* err_flag, void* stream);
+LEMOQ_API int lemoq_ep_regroup(const void* recv, int R, int H, int experts, int world, int rank, void* x_sorted, int32_t* perm,
+                     int32_t* seg, int* err_flag, void* stream);
+LEMOQ_API int lemoq_ep_return(const void* y_sorted, const int32_t* perm, const int32_t* seg, int R, int H, int epr, void* y, void* stream);
+LEMOQ_API int lemoq_ep_combine(const void* back, const int32_t* slot, const void* top_w, int T, int K, int H, void* out, void* stream);
+
+/* ---------------------------------------------------------------------------
  * RMSNorm, HF-OLMoE rounding: y = fp16(x * rsqrt(mean(x^2) + eps)) * w (fp16 mul).
  * ref: src/lemoq/kernels/rmsnorm.py:102 (rms_norm_fused).
  * x, y: (rows, H) fp16; w: (H,) fp16.  H % 8 == 0, H <= 8192.

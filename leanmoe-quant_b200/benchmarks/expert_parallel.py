@@ -184,6 +184,64 @@ def expert_parallel_moe_static(h: Any, top_w: Any, top_i: Any, *, experts: int, 
         return out.to(h.dtype)
 
 
+def expert_parallel_moe_kernels(h: Any, top_w: Any, top_i: Any, *, experts: int, world: int, rank: int,
+                                expert_fn: Callable[..., Any], group: Any = None, err_flag: Any = None,
+                                section: Any = _no_section) -> Any:
+    """:func:`expert_parallel_moe_static` for CUDA tensors with the row bookkeeping done by the library's exchange
+    kernels (``lemoq_ep_*``): two launches to fill the send slots, two to regroup what arrived by local expert (which
+    also yields the segment offsets of the expert kernels), one to give the results back, one for the weighted sum -
+    where the tensor-library form needs some forty.  Same placement of every row, same collectives, so the two forms
+    are interchangeable between ranks; the weighted sum is taken in slot order in fp32.  ``expert_fn(x_sorted, None,
+    seg_offsets=seg)`` runs this rank's experts on rows in local-expert order."""
+    import torch.distributed as dist
+
+    from lemoq import _cabi
+
+    if experts > 2048:
+        raise ValueError("experts=%d: the id column of the static exchange is fp16 (exact up to 2048)" % experts)
+    _cabi.require_cuda(h, top_w, top_i, what="expert-parallel exchange kernels")
+    t, k = int(top_i.shape[0]), int(top_i.shape[1])
+    pairs_n, hidden, epr, dev = t * k, int(h.shape[1]), experts // world, h.device
+    rows = world * pairs_n
+    stream = _cabi.current_stream(dev)
+    err = _cabi.ptr(err_flag) if err_flag is not None else None
+    h, top_i = h.contiguous(), top_i.contiguous()
+    weights = top_w.to(torch.float16).contiguous()
+    with section("dispatch-combine glue"):
+        send = torch.empty((world, pairs_n, hidden + ID_COLS), dtype=torch.float16, device=dev)
+        slot = torch.empty(pairs_n, dtype=torch.int32, device=dev)
+        src = torch.empty(rows, dtype=torch.int32, device=dev)
+        _cabi.call("lemoq_ep_dispatch", _cabi.ptr(h), _cabi.ptr(top_i), t, k, hidden, experts, world, _cabi.ptr(send), _cabi.ptr(slot),
+                   _cabi.ptr(src), err, stream)
+    if world > 1:
+        with section("all-to-all"):
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=group)
+    else:
+        recv = send
+    with section("dispatch-combine glue"):
+        x_sorted = torch.empty((rows, hidden), dtype=torch.float16, device=dev)
+        perm = torch.empty(rows, dtype=torch.int32, device=dev)
+        seg = torch.empty(epr + 1, dtype=torch.int32, device=dev)
+        _cabi.call("lemoq_ep_regroup", _cabi.ptr(recv), rows, hidden, experts, world, rank, _cabi.ptr(x_sorted), _cabi.ptr(perm),
+                   _cabi.ptr(seg), err, stream)
+    with section("expert kernels"):
+        y_sorted = expert_fn(x_sorted, None, seg_offsets=seg)
+    with section("dispatch-combine glue"):
+        y = torch.empty((world, pairs_n, hidden), dtype=torch.float16, device=dev)
+        _cabi.call("lemoq_ep_return", _cabi.ptr(y_sorted), _cabi.ptr(perm), _cabi.ptr(seg), rows, hidden, epr, _cabi.ptr(y), stream)
+    if world > 1:
+        with section("all-to-all"):
+            back = torch.empty_like(y)
+            dist.all_to_all_single(back, y, group=group)
+    else:
+        back = y
+    with section("dispatch-combine glue"):
+        out = torch.empty((t, hidden), dtype=torch.float16, device=dev)
+        _cabi.call("lemoq_ep_combine", _cabi.ptr(back), _cabi.ptr(slot), _cabi.ptr(weights), t, k, hidden, _cabi.ptr(out), stream)
+        return out.to(h.dtype)
+
+
 # ---------------------------------------------------------------------------------------------------
 # the CUDA side: this rank's experts and the batched lockstep decode step
 # ---------------------------------------------------------------------------------------------------
@@ -198,9 +256,11 @@ class LocalExperts:
         self.group_size = int(q.group_size)
         self.n = hi - lo
         hidden, ffn = int(self.gate_up.shape[2]), int(self.down.shape[2])
-        self.batched = hidden % 512 == 0 and hidden <= 2048 and ffn % 512 == 0 and ffn <= 2048
+        self.batched = hidden % 128 == 0 and hidden <= 4096 and ffn % 128 == 0 and ffn <= 4096 and self.group_size % 128 == 0
 
-    def __call__(self, x: Any, local_ids: Any) -> Any:
+    def __call__(self, x: Any, local_ids: Any, seg_offsets: Any = None) -> Any:
+        """``x (R, H)`` rows in local-expert order with either their ``local_ids (R,)`` or the ``seg_offsets`` of the
+        experts' segments (the exchange kernels hand these over); returns the unweighted expert outputs ``(R, H)``."""
         from lemoq import _cabi
         from lemoq.kernels.batched_w8 import w8_experts_tokens
 
@@ -208,7 +268,9 @@ class LocalExperts:
         if self.batched:
             # weights-stationary kernels: every resident expert's rows are read once for all its pairs
             return w8_experts_tokens(x, local_ids, self.gate_up, self.gate_up_scale, self.down, self.down_scale,
-                                     group_size=self.group_size)
+                                     group_size=self.group_size, seg_offsets=seg_offsets)
+        if local_ids is None:
+            raise NotImplementedError("expert shapes outside the many-token kernels need the row ids (use the tensor-library exchange)")
         r, hidden = int(x.shape[0]), int(x.shape[1])
         ffn = int(self.down.shape[2])
         ids = local_ids.to(torch.int64).reshape(r, 1).contiguous()
@@ -230,7 +292,7 @@ class ExpertParallelDecoder:
     ``StaticCacheDecodeSession`` on it whose prefill filled the fp16 cache for the common prompt."""
 
     def __init__(self, model: Any, session: Any, *, sequences: int, world: int, rank: int, group: Any = None,
-                 attn_splits: int = 4, static_exchange: bool = False) -> None:
+                 attn_splits: int = 4, static_exchange: bool = False, exchange_kernels: bool = True) -> None:
         from lemoq import _cabi
 
         if sequences % world != 0:
@@ -247,6 +309,8 @@ class ExpertParallelDecoder:
         self.position = int(session.position)
         self.splits = attn_splits
         self.static_exchange = static_exchange
+        # the static exchange with the library's row kernels (default) or written with tensor-library calls
+        self.exchange_kernels = bool(exchange_kernels and static_exchange)
         self.graph = None
         epr = cfg.num_experts // world
         self.local = [LocalExperts(layer.mlp._static_experts, rank * epr, (rank + 1) * epr) for layer in model.model.layers]
@@ -378,6 +442,9 @@ class ExpertParallelDecoder:
         cos_row = self.cos.index_select(0, self.pos_t).reshape(-1).contiguous()
         sin_row = self.sin.index_select(0, self.pos_t).reshape(-1).contiguous()
         moe_fn = expert_parallel_moe_static if self.static_exchange else expert_parallel_moe
+        if self.exchange_kernels and all(le.batched for le in self.local):
+            def moe_fn(*args, **kwargs):  # noqa: E306
+                return expert_parallel_moe_kernels(*args, err_flag=self.err, **kwargs)
         x = self.model.model.embed_tokens.weight[tokens]  # (b, H) fp16
         eps = float(cfg.rms_norm_eps)
         sec = self._section

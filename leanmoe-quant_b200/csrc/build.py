@@ -15,7 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ["cabi.cu", "gemv_w8.cu", "stream_gemv.cu", "moe_grouped.cu", "attn_decode.cu", "small_ops.cu", "step.cu", "step_tile.cu", "batched_w8.cu"]
+SOURCES = ["cabi.cu", "gemv_w8.cu", "stream_gemv.cu", "moe_grouped.cu", "attn_decode.cu", "small_ops.cu", "step.cu", "step_tile.cu", "batched_w8.cu", "ep_exchange.cu"]
 HEADERS = ["common.cuh", "gemv_common.cuh", "stream.cuh", "stream_gemv.cuh", "step_kernel.h", "kernels.h", os.path.join(ROOT, "include", "lemoq_b200.h")]
 LIB = os.path.join(HERE, "liblemoq_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

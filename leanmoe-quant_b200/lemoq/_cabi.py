@@ -67,6 +67,11 @@ _SIGNATURES = {
     "lemoq_w8_quantise_tokens": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "lemoq_w8_rows_tokens": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                      c_void_p, c_void_p]),
+    "lemoq_ep_dispatch": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p]),
+    "lemoq_ep_regroup": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lemoq_ep_return": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "lemoq_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "lemoq_attn_static_scratch_bytes": (c_size_t, []),
     "lemoq_attn_decode_int8_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                               c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
