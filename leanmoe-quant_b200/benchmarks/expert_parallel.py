@@ -548,6 +548,9 @@ def measure(model: Any, *, device: str, world: int, rank: int, sequences: int = 
         hist = torch.cat(gathered, dim=0)
     parts = dec.timing_split(tokens) if split else None
     flags = dec.error_flags()
+    alone_ms = None
+    if world > 1 and graph and exchange == "static":
+        alone_ms = _collectives_alone_ms(dec, model.config, world, device, barrier)
     # a captured graph holds collective kernels of the process group: destroy it (not only drop the name) before
     # anybody tears the communicator down, whose shutdown waits for every captured plan to be released
     if dec.graph is not None:
@@ -566,7 +569,49 @@ def measure(model: Any, *, device: str, world: int, rank: int, sequences: int = 
                                    "NCCL all-to-all dispatch/combine (benchmark configuration 5)" % (sequences, ctx, cfg.num_experts // world),
                        "layers": cfg.num_hidden_layers, "identical_sequences": bool(identical), "exchange": exchange,
                        "cuda_graph": bool(graph), "all_to_alls_per_step": 2 * cfg.num_hidden_layers if world > 1 else 0},
-            "eager_split_us_per_step": parts, "error_flags": flags, "token_digest": token_digest(hist), "tokens": hist.cpu()}
+            "eager_split_us_per_step": parts, "all_to_alls_alone_ms_per_step": alone_ms, "error_flags": flags,
+            "token_digest": token_digest(hist), "tokens": hist.cpu()}
+
+
+def _collectives_alone_ms(dec: Any, cfg: Any, world: int, device: str, barrier: Callable[[], None], iters: int = 5) -> float:
+    """Device time of the all-to-alls of one step ALONE, in a CUDA graph of their own: same buffers shapes, same count
+    (two per layer), nothing in between.  What the step cannot get below at this world size.  Max over ranks."""
+    import torch.distributed as dist
+
+    pairs = dec.b * int(cfg.num_experts_per_tok)
+    hidden = int(cfg.hidden_size)
+    send = torch.zeros((world, pairs, hidden + ID_COLS), dtype=torch.float16, device=device)
+    recv = torch.empty_like(send)
+    y = torch.zeros((world, pairs, hidden), dtype=torch.float16, device=device)
+    back = torch.empty_like(y)
+
+    def exchanges():
+        for _ in range(int(cfg.num_hidden_layers)):
+            dist.all_to_all_single(recv, send, group=dec.group)
+            dist.all_to_all_single(back, y, group=dec.group)
+
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        exchanges()
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        exchanges()
+    g.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=device, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    g.reset()  # before anybody tears the communicator down (see measure())
+    del g
+    return float(ms.item())
 
 
 def shutdown_process_group(limit_s: float = 60.0) -> None:
