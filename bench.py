@@ -533,12 +533,19 @@ def run_gpu(args) -> int:
     torch.cuda.empty_cache()
     full_size = args.layers is None
     if not args.no_sub_records and full_size:
+        def guarded(fn, *fn_args):
+            """A sub-record that fails is reported as such; the headline line is printed whatever happens to them."""
+            try:
+                return fn(*fn_args)
+            except Exception as exc:  # noqa: BLE001
+                return {"error": "%s: %s" % (type(exc).__name__, exc)}
+
         if rank == 0 and ctx != 4096:
-            result["ctx4096"] = sub_ctx4096(model, peaks, device)
+            result["ctx4096"] = guarded(sub_ctx4096, model, peaks, device)
         if rank == 0:
-            result["config4"] = sub_config4(peaks)
+            result["config4"] = guarded(sub_config4, peaks)
         barrier()
-        ep_rec = sub_expert_parallel(model, device, world, rank)  # every rank takes part
+        ep_rec = guarded(sub_expert_parallel, model, device, world, rank)  # every rank takes part
         if rank == 0:
             result["expert_parallel"] = ep_rec
     if rank == 0:

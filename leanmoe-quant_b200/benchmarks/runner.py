@@ -119,8 +119,9 @@ def build_model(*, layers: int | None = None, seed: int = 0, device: str = "cuda
 
 
 def install_replacements(model: Any, *, attn: str | None, moe: str, quant_cfg: dict[str, Any] | None, rmsnorm: str,
-                         ctx: int, max_new_tokens: int, device: str = "cuda") -> dict[str, Any]:
-    """The reference's install order, all before capture."""
+                         ctx: int, max_new_tokens: int, device: str = "cuda", prequantized: dict[int, Any] | None = None) -> dict[str, Any]:
+    """The reference's install order, all before capture.  ``prequantized`` (layer -> ``QuantFusedExperts``, e.g. from
+    ``lemoq.quant.expert_calibration.load_bundle``) supplies the experts ready-made instead of quantising them here."""
     import torch
 
     from lemoq.kernels.attn_decode import replace_attention_cores, warm as warm_attn
@@ -134,7 +135,11 @@ def install_replacements(model: Any, *, attn: str | None, moe: str, quant_cfg: d
     qspec = quant_spec_for_cfg(quant_cfg) if quant_cfg else None
     if moe != "hf":
         impl = "gather" if moe in ("static", "gather") else "grouped"
-        info["moe_replaced"] = replace_moe_blocks(model, impl=impl, quant=qspec)
+        if prequantized is not None:
+            info["moe_replaced"] = replace_moe_blocks(model, impl=impl, prequantized=prequantized)
+            info["experts_from_bundle"] = True
+        else:
+            info["moe_replaced"] = replace_moe_blocks(model, impl=impl, quant=qspec)
     if qspec is not None:
         _, report = quantize_model(model, qspec)
         info["quantize_report"] = report.to_dict()

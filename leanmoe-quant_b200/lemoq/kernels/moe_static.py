@@ -192,6 +192,14 @@ def replace_moe_blocks(model: Any, *, verbose: bool = False, impl: str = "gather
             raise ValueError("prequantized requires grouped and forbids re-quantization")
         if sorted(prequantized) != list(range(len(decoder_layers))):
             raise ValueError("prequantized must cover all model layers exactly")
+        # every payload is checked before the first block is touched: a bad one leaves the model as it was
+        from lemoq.quant.expert_calibration import validate_packed
+
+        for index, layer in enumerate(decoder_layers):
+            members = getattr(getattr(layer, "mlp", None), "experts", None)
+            if members is not None:
+                validate_packed(prequantized[index], experts=len(members), hidden=int(members[0].gate_proj.in_features),
+                                ffn=int(members[0].down_proj.in_features))
     count = 0
     for index, layer in enumerate(decoder_layers):
         block = getattr(layer, "mlp", None)
