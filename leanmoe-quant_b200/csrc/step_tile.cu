@@ -326,6 +326,11 @@ struct AttnSm {
     __align__(16) uint32_t newv[32];
     float qsx;
     unsigned short newks, newvs;  // fp16 bit patterns of the new row's scales
+    // fp16-KV arm: the query as it is (fp16 after RoPE), the new token's K and V rows, the softmax weights of a tile
+    __align__(16) __half q16[kHeadDim];
+    __align__(16) uint2 newk16[32];
+    __align__(16) uint2 newv16[32];
+    float p32[kStreamWarps][32];
 };
 
 // Sizes, shifts and this block's place in the grid (all row widths are powers of two between 512 and 2048).
@@ -342,6 +347,8 @@ struct Geo {
     int h, split;   // this block's (head, split) unit
     int tile0;      // first KV tile of this block's slice
     int owner;      // the slice contains the new token: this block writes its K/V row
+    int kvt;        // cached positions per KV tile: 64 (int8 codes) or 32 (fp16 values); 8 KB of keys + 8 KB of values either way
+    int kv16;       // the cache is read as fp16 (no int8 mirror)
     int has_unit;   // this block has a unit at all
     int nt[8];      // tiles of this block per kind (index 6: the lm_head tiles)
 };
@@ -381,14 +388,16 @@ __device__ __noinline__ void issue_tile(const Smem& S, int layer, int kind, int 
     const int lane = threadIdx.x & 31;
     const char* src = nullptr;
     uint32_t bytes = 0, dst = 0, tx = 0;
-    if (kind == KB) {  // cached positions of this block's head: key codes and value codes (the consumer reads the scales itself)
-        const int first = (geo.tile0 + lt) * kKvTile;
-        const uint32_t npos = static_cast<uint32_t>(min(kKvTile, geo.S - first));  // the last tile of a head may be short
+    if (kind == KB) {  // cached positions of this block's head: keys and values (int8: the consumer reads the scales itself)
+        const int first = (geo.tile0 + lt) * geo.kvt;
+        const uint32_t npos = static_cast<uint32_t>(min(geo.kvt, geo.S - first));  // the last tile of a head may be short
         const uint32_t p0 = static_cast<uint32_t>(geo.h * geo.S + first);
-        tx = 2 * npos * kHeadDim;
+        const uint32_t row = geo.kv16 ? 2 * kHeadDim : kHeadDim;  // bytes of a position
+        tx = 2 * npos * row;
         if (lane < 2) {
-            src = reinterpret_cast<const char*>(lane == 0 ? L.kc : L.vc) + static_cast<size_t>(p0) * kHeadDim;
-            bytes = npos * kHeadDim;
+            const void* base = geo.kv16 ? static_cast<const void*>(lane == 0 ? L.keys : L.values) : static_cast<const void*>(lane == 0 ? L.kc : L.vc);
+            src = reinterpret_cast<const char*>(base) + static_cast<size_t>(p0) * row;
+            bytes = npos * row;
             dst = lane * kKvTile * kHeadDim;
         }
     } else if (kind == KD) {  // 4 router rows (fp16) in one copy; fewer than 4 experts left: only those
@@ -833,7 +842,13 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
             for (int j = 0; j < 4; ++j) f[j] = __half2float(rh[j]);
         }
         if (!good && p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
-        if (warp == 0) {
+        if (warp == 0 && geo.kv16) {  // the query as fp16 (exact: it was rounded after the rotation); scores are scaled in fp32
+            __half2 h01 = __floats2half2_rn(f[0], f[1]), h23 = __floats2half2_rn(f[2], f[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&h01);
+            o.y = *reinterpret_cast<uint32_t*>(&h23);
+            *reinterpret_cast<uint2*>(sm.q16 + lane * 4) = o;
+        } else if (warp == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) f[j] *= p.qk_scale_log2;
             const float amax = warp_max(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))));
@@ -852,20 +867,24 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
             o.x = *reinterpret_cast<uint32_t*>(&h01);
             o.y = *reinterpret_cast<uint32_t*>(&h23);
             *reinterpret_cast<uint2*>((warp == 1 ? L.keys : L.values) + at) = o;
-            const float amax = warp_max(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))));
-            const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-            uint32_t packed = 0;
+            if (geo.kv16) {  // the fp16 cache is what attention reads: keep the row for the tile that holds the new slot
+                (warp == 1 ? sm.newk16 : sm.newv16)[lane] = o;
+            } else {  // the int8 mirror: quantise the row, write codes and scale, keep both
+                const float amax = warp_max(fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3]))));
+                const float sc = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+                uint32_t packed = 0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int c = static_cast<int>(fminf(fmaxf(rintf(__fdiv_rn(f[j], sc)), -127.0f), 127.0f));
-                packed |= (static_cast<uint32_t>(c) & 0xffu) << (8 * j);
-            }
-            *reinterpret_cast<uint32_t*>((warp == 1 ? L.kc : L.vc) + at) = packed;
-            (warp == 1 ? sm.newk : sm.newv)[lane] = packed;
-            if (lane == 0) {
-                const __half hs = __float2half_rn(sc);
-                (warp == 1 ? L.ks : L.vs)[static_cast<int64_t>(h) * geo.S + geo.pos] = hs;
-                (warp == 1 ? sm.newks : sm.newvs) = __half_as_ushort(hs);
+                for (int j = 0; j < 4; ++j) {
+                    const int c = static_cast<int>(fminf(fmaxf(rintf(__fdiv_rn(f[j], sc)), -127.0f), 127.0f));
+                    packed |= (static_cast<uint32_t>(c) & 0xffu) << (8 * j);
+                }
+                *reinterpret_cast<uint32_t*>((warp == 1 ? L.kc : L.vc) + at) = packed;
+                (warp == 1 ? sm.newk : sm.newv)[lane] = packed;
+                if (lane == 0) {
+                    const __half hs = __float2half_rn(sc);
+                    (warp == 1 ? L.ks : L.vs)[static_cast<int64_t>(h) * geo.S + geo.pos] = hs;
+                    (warp == 1 ? sm.newks : sm.newvs) = __half_as_ushort(hs);
+                }
             }
         }
     }
@@ -976,6 +995,61 @@ __device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, co
     for (int j = 0; j < 4; ++j) acc[j] = fmaf(static_cast<float>(ai[j]), back, acc[j]);
 }
 
+// One KV tile of the fp16-KV arm (32 positions in a stage: 8 KB of keys, 8 KB of values): a lane owns one position
+// for the scores (its key row against the query, 16-byte chunks taken in a rotated order so that the eight lanes of a
+// quarter warp hit different banks), online softmax (base 2), then four output dimensions for the values.
+__device__ __forceinline__ void attention_tile16(unsigned char* st, AttnSm& sm, const Geo& geo, int lt, int lane, int warp, float qk_scale_log2,
+                                                 float& m_i, float& l_i, float (&acc)[4]) {
+    constexpr int D = kHeadDim, T = 32;
+    const int base = (geo.tile0 + lt) * T;
+    const int nvalid = min(T, geo.nf - base);
+    if (geo.owner && geo.pos >= base && geo.pos < base + T) {
+        // the row of the new token: what this block has just written (the copy may have read the slot before the write)
+        const int row = geo.pos - base;
+        reinterpret_cast<uint2*>(st + row * 2 * D)[lane] = sm.newk16[lane];
+        reinterpret_cast<uint2*>(st + kKvTile * D + row * 2 * D)[lane] = sm.newv16[lane];
+        __syncwarp();
+    }
+    float dot = 0.f;
+    const unsigned char* krow = st + lane * 2 * D;
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+        const int cc = (c + lane) & 15;
+        const uint4 kv = *reinterpret_cast<const uint4*>(krow + cc * 16);
+        const uint4 qv = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sm.q16) + cc * 16);
+        const __half2* kh = reinterpret_cast<const __half2*>(&kv);
+        const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 kf = __half22float2(kh[j]), qf = __half22float2(qh[j]);
+            dot = fmaf(kf.x, qf.x, dot);
+            dot = fmaf(kf.y, qf.y, dot);
+        }
+    }
+    const float s = lane < nvalid ? dot * qk_scale_log2 : -INFINITY;
+    const float m_new = fmaxf(m_i, warp_max(s));  // finite: position 0 of the tile is valid
+    const float alpha = exp2f(m_i - m_new);
+    const float pj = s > -INFINITY ? exp2f(s - m_new) : 0.f;
+    l_i = fmaf(l_i, alpha, warp_sum(pj));
+    m_i = m_new;
+    sm.p32[warp][lane] = pj;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] *= alpha;
+    const unsigned char* vcol = st + kKvTile * D + lane * 8;
+#pragma unroll 8
+    for (int j = 0; j < nvalid; ++j) {  // rows behind the filled length are not numbers that may be multiplied by zero
+        const float w = sm.p32[warp][j];
+        const uint2 vv = *reinterpret_cast<const uint2*>(vcol + j * 2 * D);
+        const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vv.x)), v23 = __half22float2(*reinterpret_cast<const __half2*>(&vv.y));
+        acc[0] = fmaf(w, v01.x, acc[0]);
+        acc[1] = fmaf(w, v01.y, acc[1]);
+        acc[2] = fmaf(w, v23.x, acc[2]);
+        acc[3] = fmaf(w, v23.y, acc[3]);
+    }
+    __syncwarp();
+}
+
 // Merge of the block's warps into the unit's partial (m, l, acc[128]).
 __device__ __noinline__ void attention_partial(const StepParams& p, Smem& S) {
     constexpr int D = kHeadDim;
@@ -1063,7 +1137,9 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
             geo.f_blocks = count_of(p.H / 8, b, G);
             const bool has_unit = b < p.heads * p.splits;
             const int unit = has_unit ? b : 0;
-            const int ntile_total = (nf + kKvTile - 1) / kKvTile;
+            geo.kv16 = p.kv_int8 ? 0 : 1;
+            geo.kvt = p.kv_int8 ? kKvTile : kKvTile / 2;
+            const int ntile_total = (nf + geo.kvt - 1) / geo.kvt;
             const int tps = (ntile_total + p.splits - 1) / p.splits;
             geo.h = unit / p.splits;
             geo.split = unit - geo.h * p.splits;
@@ -1072,7 +1148,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
             geo.has_unit = has_unit ? 1 : 0;
             geo.tile0 = geo.split * tps;
             const int tile1 = min(geo.tile0 + tps, ntile_total);
-            const int ptile = static_cast<int>(pos) / kKvTile;
+            const int ptile = static_cast<int>(pos) / geo.kvt;
             geo.owner = has_unit && pos_ok && pos < nf && ptile >= geo.tile0 && ptile < tile1;
             geo.nt[KA] = count_of(3 * A / 8, b, G);
             geo.nt[KB] = has_unit && tile1 > geo.tile0 ? tile1 - geo.tile0 : 0;
@@ -1167,6 +1243,13 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
                     for (int lt = lt0; lt < ntiles; lt += kStreamWarps) {
+                        if (geo.kv16) {
+                            if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
+                            c_par ^= 1u;
+                            attention_tile16(my_stage, sm, geo, lt, lane, warp, p.qk_scale_log2, m_i, l_i, acc);
+                            stage_release(empty_bar);
+                            continue;
+                        }
                         // the scales of the tile's positions (two per lane), requested before the wait for the codes
                         float kscale[2], vscale[2];
 #pragma unroll
@@ -1424,7 +1507,7 @@ bool tile_eligible(const lemoq_step_desc& d) {
     if (d.group_size != 128) return false;
     auto ok_dim = [](int n) { return n == 512 || n == 1024 || n == 2048; };  // row widths: powers of two, halves of whole 128-groups
     if (!ok_dim(d.hidden) || !ok_dim(A) || !ok_dim(d.ffn)) return false;
-    if (d.head_dim != tile::kHeadDim || !d.kv_int8) return false;  // the fp16-KV arm runs as chained kernels
+    if (d.head_dim != tile::kHeadDim) return false;
     if (d.experts > 128 || d.top_k > 32 || d.top_k > d.experts) return false;
     if (d.top_k * d.ffn > 8192) return false;                      // planes of the routed experts' activations
     if (d.vocab % 8 != 0 || d.layers + 1 > tile::kMaxLayers) return false;
@@ -1434,7 +1517,8 @@ bool tile_eligible(const lemoq_step_desc& d) {
 // Attention splits per head for the tile form: every (head, split) unit should have at most one KV tile per
 // streaming warp.
 int tile_attention_splits(const lemoq_step_desc& d, int grid) {
-    const int tiles = (d.max_len + tile::kKvTile - 1) / tile::kKvTile;
+    const int kvt = d.kv_int8 ? tile::kKvTile : tile::kKvTile / 2;  // positions per 16 KB tile
+    const int tiles = (d.max_len + kvt - 1) / kvt;
     int s = (tiles + tile::kStreamWarps - 1) / tile::kStreamWarps;
     s = std::max(1, std::min(s, tile::kMaxSplits));
     return std::max(1, std::min(s, grid / d.heads));

@@ -197,6 +197,44 @@ def test_small_model_fp16_kv_arm(monkeypatch):
     session.close()
 
 
+def test_small_model_whole_step_kernel_fp16_kv_odd_capacity(monkeypatch):
+    """The whole-step kernel attending to the fp16 cache (kv_int8 off): KV tiles of 32 positions, a capacity (67) that
+    leaves the last tile of every head three rows long, the new token's row patched in from the block that wrote it."""
+    from benchmarks.cudagraph import StaticCacheDecodeSession, compare_logits
+
+    monkeypatch.setenv("LEMOQ_KV_INT8", "0")
+    spec = _small_whole_step_spec()
+    ctx, new = 61, 6
+    wf = glue.random_float_weights(spec, seed=6, dtype=torch.float16, std=0.05, norm_weight_jitter=0.1)
+    wq = glue.quantize_weights(wf)
+    model = lemoq_model_from_oracle(wf)
+    install_canonical(model, ctx, new)
+    prompt = torch.tensor([[(11 * i + 5) % spec.vocab for i in range(ctx)]])
+    st, first_tok = _fresh_oracle_state(spec, wq, prompt[0], ctx + new)
+    session = StaticCacheDecodeSession(model, prompt.to(DEV), ctx=ctx, max_new_tokens=new, engine="step")
+    session.after_prefill = _inject_oracle_cache(st)
+    session.capture(warmup=1)
+    assert session.capture_info["kernels_per_step"] == 1 and session.capture_info["step_kernel"] == "whole-step"
+    session.reset()
+    session.current_token_id = first_tok
+    toks, logits = glue.greedy_decode(wq, st, first_tok, ctx, new, kv_int8=False)
+    got_logits, got_toks = [], []
+    for _ in range(new):
+        session.replay(synchronize=True)
+        got_logits.append(session.logits_cpu().reshape(-1))
+        got_toks.append(session.current_token_id)
+    assert session.step_error_flags() == 0
+    assert got_toks == toks
+    assert compare_logits(logits, got_logits)["kl"] < KL_GATE
+    for s_, (ref, got) in enumerate(zip(logits, got_logits)):
+        assert rel_err(got, ref) < 5 * PER_KERNEL_REL_TOL, s_
+    # the rows the step wrote into the fp16 cache are the oracle's up to the rounding the activations carry
+    for i, cl in enumerate(session.cache.layers):
+        assert rel_err(cl.keys[:, :, ctx:ctx + new], st.keys[i][:, :, ctx:ctx + new]) < 2e-2, i
+        assert rel_err(cl.values[:, :, ctx:ctx + new], st.values[i][:, :, ctx:ctx + new]) < 2e-2, i
+    session.close()
+
+
 @pytest.fixture
 def whole_step_kernel():
     """The step engine as the single cooperative kernel (the default when the shapes allow it)."""
@@ -296,10 +334,16 @@ def test_full_model_whole_step_kernel_ctx_4096(whole_step_kernel):
     _full_model_greedy(4096, expect_kernels=1)
 
 
-def test_full_model_fp16_kv_arm_ctx_4096(chained_kernels, monkeypatch):
-    """Benchmark configuration 3's comparison arm: the same model attending to the fp16 cache (kv_int8 off)."""
+def test_full_model_fp16_kv_arm_ctx_4096(whole_step_kernel, monkeypatch):
+    """Benchmark configuration 3's comparison arm: the same model attending to the fp16 cache (kv_int8 off), as one
+    kernel per step."""
     monkeypatch.setenv("LEMOQ_KV_INT8", "0")
-    _full_model_greedy(4096, expect_kernels=None, kv_int8=False, steps=16)
+    _full_model_greedy(4096, expect_kernels=1, kv_int8=False, steps=16)
+
+
+def test_full_model_fp16_kv_arm_ctx_4096_chained_kernels(chained_kernels, monkeypatch):
+    monkeypatch.setenv("LEMOQ_KV_INT8", "0")
+    _full_model_greedy(4096, expect_kernels=None, kv_int8=False, steps=8)
 
 
 def _full_model_greedy(ctx, expect_kernels, kv_int8=True, steps=32):
