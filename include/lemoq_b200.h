@@ -57,7 +57,11 @@ LEMOQ_API const char* lemoq_last_error(void);
  *   key 1  warps per block of the streaming kernels (1..16)
  *   key 4  step engine: 1 (default) the whole-step cooperative kernel when the shapes allow it,
  *          0 chained per-op kernels; takes effect at the next lemoq_step_create
- * Every setting gives the same results up to fp32 summation order.
+ *   key 5  whole-step kernel, current device: polls of a flagged word before a wait gives up with
+ *          LEMOQ_FLAG_WAIT_TIMEOUT (1 .. 2^24, default 2^21).  A step whose wait ran out has gone on with
+ *          stale values: its results are void, the flag says so, the next step is unaffected.  Exists so
+ *          that the time-out path can be exercised (value 1) without anything hanging.
+ * Keys 0, 1 and 4 give the same results up to fp32 summation order.
  * No counterpart in the reference, whose tile configs are module dicts
  * (ref: src/lemoq/kernels/moe_grouped.py:78, src/lemoq/kernels/_dequant_triton.py:83).
  */

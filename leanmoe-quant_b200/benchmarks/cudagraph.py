@@ -472,6 +472,17 @@ class StaticCacheDecodeSession:
         self.torch.cuda.synchronize()
         return int(self._step["workspace"][off: off + 4].view(self.torch.int32).item())
 
+    def clear_step_error_flags(self) -> None:
+        """Zero the step engine's flag word (the flags are sticky: a step never clears what an earlier one raised)."""
+        if self._step is None:
+            return
+        from lemoq import _cabi
+
+        addr = _cabi.lib().lemoq_step_error_flag(self._step["handle"])
+        off = int(addr) - int(self._step["workspace"].data_ptr())
+        self.torch.cuda.synchronize()
+        self._step["workspace"][off: off + 4].zero_()
+
     def step_topk_ids(self) -> Any:
         """``(layers, top_k)`` int64 expert ids chosen in the most recent step (step engine only)."""
         if self._step is None:

@@ -50,6 +50,7 @@ struct StepParams {
 };
 
 size_t tile_smem_bytes();
+int set_flag_spin_limit(int polls);  // lemoq_set_tuning key 5 (current device)
 bool tile_eligible(const lemoq_step_desc& d);
 int tile_grid(const lemoq_step_desc& d);  // blocks to launch (one per SM), 0 = unavailable
 int tile_attention_splits(const lemoq_step_desc& d, int grid);

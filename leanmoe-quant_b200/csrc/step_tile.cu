@@ -98,7 +98,10 @@ __device__ __forceinline__ uint2 ld_cg8(const void* p) {
 // and then the load.  Buffers alternate with the layer's parity; the one grid barrier per layer that remains
 // (attention -> o_proj) keeps every block within one layer of every other, so no word is overwritten while
 // somebody still waits for its previous content.
-constexpr uint32_t kFlagSpinLimit = 1u << 21;
+constexpr uint32_t kFlagSpinLimit = 1u << 21;  // default of the limit below
+// Polls of a flagged word before a wait gives up (raising LEMOQ_FLAG_WAIT_TIMEOUT; the step then goes on with what the
+// word held).  lemoq_set_tuning key 5 changes it on the current device: the time-out path can be tested by making it 1.
+__constant__ uint32_t c_flag_spin_limit = kFlagSpinLimit;
 __device__ __forceinline__ void flag_store(unsigned long long* p, uint32_t data, uint32_t tag) {
     const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | data;
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
@@ -114,7 +117,8 @@ __device__ __forceinline__ bool tag_reached(unsigned long long w, uint32_t tag) 
 // N words of this thread (src[0..N), used where on[i]) until all carry the tag: data[i] = their data.  Bounded.
 template <int N>
 __device__ __forceinline__ bool flag_wait(const unsigned long long* src, const bool (&on)[N], uint32_t tag, uint32_t (&data)[N]) {
-    for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+    const uint32_t limit = c_flag_spin_limit;
+    for (uint32_t it = 0; it < limit; ++it) {
         unsigned long long w[N];
 #pragma unroll
         for (int i = 0; i < N; ++i) w[i] = on[i] ? flag_load(src + i) : (static_cast<unsigned long long>(tag) << 32);
@@ -561,7 +565,8 @@ __device__ __forceinline__ void warp_topk_per(const unsigned long long* logits, 
         for (int j = 0; j < PER; ++j) on[j] = lane + 32 * j < E;
         // lane-strided words: word j of this lane sits 32 words further
         bool good = true;
-        for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+        const uint32_t limit = c_flag_spin_limit;
+        for (uint32_t it = 0; it < limit; ++it) {
             good = true;
 #pragma unroll
             for (int j = 0; j < PER; ++j) {
@@ -812,7 +817,8 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
                 bool on[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) on[i] = b0 + lane + 32 * i < geo.G;
-                for (uint32_t it = 0; it < kFlagSpinLimit; ++it) {
+                const uint32_t limit = c_flag_spin_limit;
+                for (uint32_t it = 0; it < limit; ++it) {
                     bool ok = true;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -821,7 +827,7 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
                         d[i] = static_cast<uint32_t>(w);
                     }
                     if (ok) break;
-                    if (it + 1 == kFlagSpinLimit) good = false;
+                    if (it + 1 == limit) good = false;
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s += on[i] ? __uint_as_float(d[i]) : 0.f;
@@ -1502,6 +1508,13 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
 // ---------------------------------------------------------------------------------------------
 size_t tile_smem_bytes() { return sizeof(tile::Smem) + 128; }
 
+int set_flag_spin_limit(int polls) {
+    if (polls < 1 || polls > (1 << 24)) return set_error(LEMOQ_ERR_INVALID, "set_tuning: flag poll limit %d outside [1, 2^24]", polls);
+    const uint32_t v = static_cast<uint32_t>(polls);
+    const cudaError_t err = cudaMemcpyToSymbol(tile::c_flag_spin_limit, &v, sizeof(v));
+    if (err != cudaSuccess) return set_error(LEMOQ_ERR_CUDA, "set_tuning: %s", cudaGetErrorString(err));
+    return LEMOQ_OK;
+}
 bool tile_eligible(const lemoq_step_desc& d) {
     const int A = d.heads * d.head_dim;
     if (d.group_size != 128) return false;

@@ -10,6 +10,7 @@
 // Dequantisation runs on the ALU/FMA pipes (PRMT + FFMA per code, see magic_dot16), fp32
 // accumulation, one fp16 scale per 16-code lane chunk, warp-shuffle reduction, no atomics.
 #include "stream_gemv.cuh"
+#include "step_kernel.h"
 
 namespace lemoq {
 
@@ -354,6 +355,7 @@ int set_stream_tuning(int key, int value) {
         g_step_use_whole = value;
         return LEMOQ_OK;
     }
+    if (key == 5) return set_flag_spin_limit(value);
     return set_error(LEMOQ_ERR_INVALID, "set_tuning: unknown key %d or value %d out of range", key, value);
 }
 

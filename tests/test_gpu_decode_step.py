@@ -496,3 +496,46 @@ def test_out_of_range_step_scalars_raise_flags_instead_of_faulting(whole):
         session.close()
     finally:
         _cabi.call("lemoq_set_tuning", 4, 1)
+
+
+def test_a_wait_that_runs_out_raises_the_flag_and_the_next_step_is_unaffected():
+    """The time-out path of the whole-step kernel's flagged-word waits, exercised without anything hanging: with the
+    poll limit at 1 (tuning key 5) a reader gives up on the first look, the step goes on with stale values, returns,
+    and reports LEMOQ_FLAG_WAIT_TIMEOUT (8).  Every copy is still awaited and every index still comes from clamped
+    scalars or lane numbers, so nothing but the values is affected; with the limit restored the same session decodes
+    the same tokens as before."""
+    from benchmarks.cudagraph import StaticCacheDecodeSession
+    from lemoq import _cabi
+
+    spec = _small_whole_step_spec()
+    ctx, new = 40, 6
+    wf = glue.random_float_weights(spec, seed=13, dtype=torch.float16, std=0.05, norm_weight_jitter=0.1)
+    model = lemoq_model_from_oracle(wf)
+    install_canonical(model, ctx, new)
+    prompt = torch.tensor([[(3 * i + 7) % spec.vocab for i in range(ctx)]], device=DEV)
+    session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=new, engine="step")
+    session.capture(warmup=1)
+    assert session.capture_info["step_kernel"] == "whole-step"
+
+    def decode():
+        session.reset()
+        out = []
+        for _ in range(new):
+            session.replay(synchronize=True)
+            out.append(session.current_token_id)
+        return out
+
+    good = decode()
+    assert session.step_error_flags() == 0
+    try:
+        _cabi.call("lemoq_set_tuning", 5, 1)
+        session.reset()
+        session.replay(synchronize=True)  # returns: the waits are bounded
+        assert session.step_error_flags() & 8
+        assert 0 <= session.current_token_id < spec.vocab  # the pick is a valid id whatever the logits are
+    finally:
+        _cabi.call("lemoq_set_tuning", 5, 1 << 21)
+    session.clear_step_error_flags()
+    assert decode() == good
+    assert session.step_error_flags() == 0
+    session.close()
