@@ -497,7 +497,8 @@ def token_digest(hist: Any) -> str:
 
 
 def measure(model: Any, *, device: str, world: int, rank: int, sequences: int = 64, ctx: int = 2048, steps: int = 32,
-            warmup: int = 3, exchange: str = "static", graph: bool = True, identical: bool = False, split: bool = True) -> dict:
+            warmup: int = 3, exchange: str = "static", graph: bool = True, identical: bool = False, split: bool = True,
+            attn_splits: int | None = None) -> dict:
     """Prefill the shared prompt, build this rank's share of the lockstep decoder, decode ``warmup + steps`` tokens
     per sequence and time the last ``steps`` (device events, max over ranks).  ``model`` is the canonical quantised
     module tree.  Returns the result record (every rank; token table and digest are those of all sequences)."""
@@ -510,7 +511,8 @@ def measure(model: Any, *, device: str, world: int, rank: int, sequences: int = 
     horizon = steps + warmup + 2
     prompt = torch.full((1, ctx), 1, dtype=torch.long, device=device)
     session = StaticCacheDecodeSession(model, prompt, ctx=ctx, max_new_tokens=horizon, device=device, engine="ops")  # prefills
-    dec = ExpertParallelDecoder(model, session, sequences=sequences, world=world, rank=rank, static_exchange=exchange == "static")
+    extra = {} if attn_splits is None else {"attn_splits": int(attn_splits)}
+    dec = ExpertParallelDecoder(model, session, sequences=sequences, world=world, rank=rank, static_exchange=exchange == "static", **extra)
     if graph:
         dec.capture()
     # the literal configuration decodes identical sequences; distinct first tokens make the exchange non-trivial
@@ -651,7 +653,7 @@ def run(args: Any) -> int:
     install_replacements(model, attn="kernel", moe="grouped", quant_cfg={"bit_width": "w8a16", "dequant": "fused", "group_size": 128},
                          rmsnorm="fused", ctx=args.ctx, max_new_tokens=args.steps + args.warmup + 2, device=device)
     result = measure(model, device=device, world=world, rank=rank, sequences=args.sequences, ctx=args.ctx, steps=args.steps,
-                     warmup=args.warmup, exchange=args.exchange, graph=args.graph, identical=args.identical)
+                     warmup=args.warmup, exchange=args.exchange, graph=args.graph, identical=args.identical, attn_splits=args.attn_splits)
     hist = result.pop("tokens")
     if rank == 0:
         if args.check_against:
@@ -676,6 +678,7 @@ def main() -> int:
     ap.add_argument("--exchange", default="static", choices=["static", "dynamic"],
                     help="static: fixed-capacity all-to-all, nothing read on the host; dynamic: counts exchanged and read per layer")
     ap.add_argument("--graph", action="store_true", help="capture the step (with its all-to-alls) in one CUDA graph; static exchange only")
+    ap.add_argument("--attn-splits", type=int, default=None, help="splits of the key range per (sequence, head) in the attention kernel")
     ap.add_argument("--identical", action="store_true", help="all sequences start from the prompt's own next token")
     ap.add_argument("--tokens-out", default=None, help="rank 0 saves the (sequences, warmup+steps) decoded tokens here")
     ap.add_argument("--check-against", default=None, help="a --tokens-out file of another world size: must match token for token")
