@@ -197,6 +197,55 @@ def test_small_model_fp16_kv_arm(monkeypatch):
     session.close()
 
 
+SHAPES = {
+    # every row width 1024, expert rows of 2048 (one routed expert per down tile), renormalised routing weights
+    "wide-ffn-renorm": dict(layers=2, hidden=1024, heads=8, head_dim=128, experts=16, top_k=4, ffn=2048, vocab=1000, norm_topk_prob=True),
+    # 128 experts (four per lane in the routing warp), sixteen routed: the activation planes are at their 8192-value limit
+    "many-experts": dict(layers=2, hidden=512, heads=4, head_dim=128, experts=128, top_k=16, ffn=512, vocab=1024),
+    # one routed expert (no pairing of experts in a down tile), full hidden width, three layers
+    "one-expert": dict(layers=3, hidden=2048, heads=16, head_dim=128, experts=8, top_k=1, ffn=1024, vocab=2048),
+}
+
+
+@pytest.mark.parametrize("shape", sorted(SHAPES))
+def test_whole_step_kernel_other_shapes(shape):
+    """Shapes at the corners of what the whole-step kernel takes, against the oracle from identical caches: tokens,
+    logits, and the expert ids (exact against the oracle's routing of the step's OWN router logits)."""
+    from benchmarks.cudagraph import StaticCacheDecodeSession, compare_logits
+
+    spec = glue.OlmoeSpec(**SHAPES[shape])
+    ctx, new = 70, 5
+    wf = glue.random_float_weights(spec, seed=31, dtype=torch.float16, std=0.05, norm_weight_jitter=0.1)
+    wq = glue.quantize_weights(wf)
+    model = lemoq_model_from_oracle(wf)
+    install_canonical(model, ctx, new)
+    prompt = torch.tensor([[(17 * i + 3) % spec.vocab for i in range(ctx)]])
+    st, first_tok = _fresh_oracle_state(spec, wq, prompt[0], ctx + new)
+    glue.build_int8_mirror(st)
+    session = StaticCacheDecodeSession(model, prompt.to(DEV), ctx=ctx, max_new_tokens=new, engine="step")
+    session.after_prefill = _inject_oracle_cache(st)
+    session.capture(warmup=1)
+    assert session.capture_info["kernels_per_step"] == 1 and session.capture_info["step_kernel"] == "whole-step", shape
+    session.reset()
+    session.current_token_id = first_tok
+    toks, logits = glue.greedy_decode(wq, st, first_tok, ctx, new, kv_int8=True)
+    got_logits, got_toks = [], []
+    for _ in range(new):
+        session.replay(synchronize=True)
+        got_logits.append(session.logits_cpu().reshape(-1))
+        got_toks.append(session.current_token_id)
+        ids, own = session.step_topk_ids().cpu(), session.step_router_logits().cpu()
+        for li in range(spec.layers):
+            _, want = ops.routing_softmax_topk(own[li:li + 1], spec.top_k, spec.norm_topk_prob)
+            assert want.reshape(-1).tolist() == ids[li].tolist(), (shape, li)
+    assert session.step_error_flags() == 0
+    assert got_toks == toks, shape
+    assert compare_logits(logits, got_logits)["kl"] < KL_GATE
+    for s_, (ref, got) in enumerate(zip(logits, got_logits)):
+        assert rel_err(got, ref) < 5 * PER_KERNEL_REL_TOL, (shape, s_)
+    session.close()
+
+
 def test_small_model_whole_step_kernel_fp16_kv_odd_capacity(monkeypatch):
     """The whole-step kernel attending to the fp16 cache (kv_int8 off): KV tiles of 32 positions, a capacity (67) that
     leaves the last tile of every head three rows long, the new token's row patched in from the block that wrote it."""
