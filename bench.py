@@ -319,8 +319,9 @@ def sub_ctx4096(model, peaks, device: str, steps: int = 64) -> dict:
 
 def sub_config4(peaks) -> dict:
     """Benchmark configuration 4 and the per-kernel rows: the isolated, L2-flushed microbenchmarks of
-    benchmarks/bench_kernels.py (grouped MoE at 1/4/16 tokens with int8 and fp16 weights, dense W8 GEMV at the
-    q.k.v / o_proj / lm_head shapes, attention at ctx 1024 / 4096)."""
+    benchmarks/bench_kernels.py (grouped MoE at 1/4/16 tokens with int8 and fp16 weights, dense W8 rows at the
+    q.k.v / o_proj / lm_head shapes for one token and, with the many-token kernel, for 16 and 64, attention at
+    ctx 1024 / 4096 for three split counts)."""
     import contextlib
     import io
 
@@ -331,6 +332,7 @@ def sub_config4(peaks) -> dict:
     with contextlib.redirect_stdout(buf):
         bk.bench_moe(timer, [1, 4, 16], peaks["hbm_gbs"])
         bk.bench_dense(timer, peaks["hbm_gbs"])
+        bk.bench_dense_tokens(timer, peaks["hbm_gbs"])
         bk.bench_attn(timer, peaks["hbm_gbs"])
     rows = []
     for line in buf.getvalue().splitlines():
@@ -338,7 +340,7 @@ def sub_config4(peaks) -> dict:
         if line.startswith("{"):
             r = json.loads(line)
             rows.append({k: r[k] for k in ("subject", "bytes", "us_cold", "gbs", "frac_of_peak", "frac_minus_floor") if k in r}
-                        | {k: r[k] for k in ("tokens", "weights", "ctx", "kv") if k in r})
+                        | {k: r[k] for k in ("tokens", "weights", "ctx", "kv", "splits") if k in r})
     return {"what": "isolated launches, 256 MB L2 flush before each, median of 10, GB/s = analytic bytes / time; "
                     "frac_minus_floor subtracts the empty event-pair time (%.1f us)" % timer.floor_us,
             "peak_gbs": peaks["hbm_gbs"], "rows": rows}
