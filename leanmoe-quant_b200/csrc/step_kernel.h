@@ -44,7 +44,6 @@ struct StepParams {
     unsigned long long *fl_x, *fl_qkv, *fl_stats, *fl_logits, *fl_act;
     int64_t* top_i;
     float* attn_part;            // (m, l, acc[D]) partial of every (head, split) unit; at the end the per-block greedy candidates
-    float* stats;                // per-block sums of squares of the q rows, then of the k rows (2 x grid floats)
     int barriers_per_launch;
     unsigned long long* stamps;  // optional: 6*layers + 2 phase time stamps of the last step
 };
