@@ -412,7 +412,11 @@ def run_gpu(args) -> int:
 
     sampler = ClockSampler(local_rank)
     # ---------------- value: device-resident inputs, K replays at advancing positions ----------------
-    session.reset()
+    torch.cuda.synchronize()
+    t_prefill = time.perf_counter()
+    session.reset()  # the eager prefill of the prompt (context only: it is not part of the metric)
+    torch.cuda.synchronize()
+    prefill_ms = (time.perf_counter() - t_prefill) * 1e3
     for _ in range(warmup):
         session.replay(synchronize=True)
     start_pos = session.position
@@ -499,7 +503,7 @@ def run_gpu(args) -> int:
         "config": workload_config(ctx, model.config.num_hidden_layers, world, byte_budget(spec, ctx + 1, CANONICAL_QUANT, kv_int8=True)["T"]),
         "run": {"engine": session.capture_info.get("engine"), "step_kernel": session.capture_info.get("step_kernel"),
                 "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0, RTN-quantised on the GPU",
-                "execution": "one CUDA graph per step"},
+                "execution": "one CUDA graph per step", "prefill_ms": round(prefill_ms, 1)},
         "ms_per_token": dev_ms, "bytes_per_step": budget["T"], "byte_floor_ms": floor_ms,
         "floor_fraction": floor_ms / dev_ms, "floor_fraction_e2e": floor_ms / e2e_ms,
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms,

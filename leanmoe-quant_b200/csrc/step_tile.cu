@@ -114,21 +114,40 @@ __device__ __forceinline__ unsigned long long flag_load(const unsigned long long
 __device__ __forceinline__ bool tag_reached(unsigned long long w, uint32_t tag) {
     return static_cast<int>(static_cast<uint32_t>(w >> 32) - tag) >= 0;
 }
+// A wait that ran out anywhere in the grid shortens every later one: every 1024 failed polls a waiting thread looks at
+// the step's flag word, where time-outs are reported, and gives up too.  (After a lost store the step thus ends within
+// milliseconds of the first time-out instead of running every wait to its limit.  The word is sticky: the host clears it.)
+__device__ __forceinline__ bool others_gave_up(const int* err_flag, uint32_t it) {
+    if ((it & 1023u) != 1023u || err_flag == nullptr) return false;
+    int v;
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(err_flag) : "memory");
+    return (v & LEMOQ_FLAG_WAIT_TIMEOUT) != 0;
+}
 // N words of this thread (src[0..N), used where on[i]) until all carry the tag: data[i] = their data.  Bounded.
 template <int N>
-__device__ __forceinline__ bool flag_wait(const unsigned long long* src, const bool (&on)[N], uint32_t tag, uint32_t (&data)[N]) {
+__device__ __forceinline__ bool flag_wait(const unsigned long long* src, const bool (&on)[N], uint32_t tag, uint32_t (&data)[N],
+                                          const int* err_flag) {
     const uint32_t limit = c_flag_spin_limit;
-    for (uint32_t it = 0; it < limit; ++it) {
-        unsigned long long w[N];
+    bool have[N];
 #pragma unroll
-        for (int i = 0; i < N; ++i) w[i] = on[i] ? flag_load(src + i) : (static_cast<unsigned long long>(tag) << 32);
+    for (int i = 0; i < N; ++i) {
+        have[i] = !on[i];
+        data[i] = 0;
+    }
+#pragma unroll 1  // one look per trip: an unrolled poll loop multiplies the traffic of everybody who waits
+    for (uint32_t it = 0; it < limit; ++it) {
         bool ok = true;
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-            ok = ok && tag_reached(w[i], tag);
-            data[i] = static_cast<uint32_t>(w[i]);
+            if (!have[i]) {  // only the words that have not arrived yet are looked at again
+                const unsigned long long w = flag_load(src + i);
+                have[i] = tag_reached(w, tag);
+                data[i] = static_cast<uint32_t>(w);
+                ok = ok && have[i];
+            }
         }
         if (ok) return true;
+        if (others_gave_up(err_flag, it)) return false;
     }
     return false;
 }
@@ -566,6 +585,7 @@ __device__ __forceinline__ void warp_topk_per(const unsigned long long* logits, 
         // lane-strided words: word j of this lane sits 32 words further
         bool good = true;
         const uint32_t limit = c_flag_spin_limit;
+#pragma unroll 1
         for (uint32_t it = 0; it < limit; ++it) {
             good = true;
 #pragma unroll
@@ -574,7 +594,7 @@ __device__ __forceinline__ void warp_topk_per(const unsigned long long* logits, 
                 good = good && tag_reached(w, tag);
                 d[j] = static_cast<uint32_t>(w);
             }
-            if (good) break;
+            if (good || others_gave_up(err_flag, it)) break;
         }
         if (!good && err_flag) atomicOr(err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
         __syncwarp();
@@ -663,7 +683,7 @@ __device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, 
             uint32_t d[8];
             const bool act = gi < ngroups;
             const bool on[8] = {act, act, act, act, act, act, act, act};
-            good = flag_wait<8>(fsrc + (act ? gi : 0) * 128 + lane16 * 8, on, tag, d) && good;
+            good = flag_wait<8>(fsrc + (act ? gi : 0) * 128 + lane16 * 8, on, tag, d, err_flag) && good;
             raw[q] = make_uint4((d[0] & 0xffffu) | (d[1] << 16), (d[2] & 0xffffu) | (d[3] << 16), (d[4] & 0xffffu) | (d[5] << 16),
                                 (d[6] & 0xffffu) | (d[7] << 16));
             if (q == 0 && ngroups <= kPerPass) break;
@@ -675,7 +695,7 @@ __device__ __noinline__ void prepare(float eps, const __half* __restrict__ src, 
             uint32_t d[4];
             const bool act = gi < ngroups;
             const bool on[4] = {act, act, act, act};
-            good = flag_wait<4>(fsrc + (act ? gi : 0) * 64 + lane16 * 4, on, tag, d) && good;
+            good = flag_wait<4>(fsrc + (act ? gi : 0) * 64 + lane16 * 4, on, tag, d, err_flag) && good;
             raw[q] = make_uint4(d[0], d[1], d[2], d[3]);
         }
     }
@@ -802,7 +822,7 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
         // this lane's four values of the head's q (k, v) row: flagged words written by the q.k.v phase
         uint32_t d4[4];
         const bool on4[4] = {true, true, true, true};
-        bool good = flag_wait<4>(fqkv + warp * A + h * D + lane * 4, on4, tag, d4);
+        bool good = flag_wait<4>(fqkv + warp * A + h * D + lane * 4, on4, tag, d4, p.err_flag);
         const uint2 raw = make_uint2((d4[0] & 0xffffu) | (d4[1] << 16), (d4[2] & 0xffffu) | (d4[3] << 16));
         const __half* rh = reinterpret_cast<const __half*>(&raw);
         float f[4];
@@ -818,6 +838,7 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
 #pragma unroll
                 for (int i = 0; i < 4; ++i) on[i] = b0 + lane + 32 * i < geo.G;
                 const uint32_t limit = c_flag_spin_limit;
+#pragma unroll 1
                 for (uint32_t it = 0; it < limit; ++it) {
                     bool ok = true;
 #pragma unroll
@@ -827,7 +848,10 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
                         d[i] = static_cast<uint32_t>(w);
                     }
                     if (ok) break;
-                    if (it + 1 == limit) good = false;
+                    if (it + 1 == limit || others_gave_up(p.err_flag, it)) {
+                        good = false;
+                        break;
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s += on[i] ? __uint_as_float(d[i]) : 0.f;
@@ -1211,7 +1235,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
         if (tid == 0) {
             unsigned int n = 0;
             while (static_cast<int>(ld_acquire_u32(p.bar_counter) - bar_target) < 0) {
-                if (++n > kBarrierSpinLimit) {
+                if (++n > kBarrierSpinLimit || others_gave_up(p.err_flag, n)) {
                     if (p.err_flag) atomicOr(p.err_flag, LEMOQ_FLAG_WAIT_TIMEOUT);
                     break;
                 }
