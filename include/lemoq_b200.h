@@ -333,7 +333,7 @@ typedef struct lemoq_step_desc {
     const int64_t* cache_position; /* device scalar: its cache slot                         */
     const int32_t* filled_len;     /* device scalar: cache_position + 1                     */
     void* logits;           /* (vocab) fp16 output                                          */
-    void* workspace;        /* lemoq_step_workspace_bytes() bytes, zeroed once by the caller */
+    void* workspace;        /* lemoq_step_workspace_bytes() bytes, 32-byte aligned, zeroed once by the caller */
     size_t workspace_bytes;
     int64_t* next_token;    /* optional device scalar: the step also writes argmax(logits) here (the
                                first maximal index, as the reference's greedy loop picks it:

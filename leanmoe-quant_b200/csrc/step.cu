@@ -166,7 +166,8 @@ extern "C" int lemoq_step_create(const lemoq_step_desc* desc, const lemoq_layer_
     const size_t need = carve(*desc, splits, nullptr);
     LEMOQ_REQUIRE(desc->workspace_bytes >= need, LEMOQ_ERR_INVALID, "step_create: workspace has %zu bytes, %zu needed",
                   desc->workspace_bytes, need);
-    LEMOQ_REQUIRE(aligned16(desc->workspace), LEMOQ_ERR_INVALID, "step_create: workspace must be 16-byte aligned");
+    LEMOQ_REQUIRE(reinterpret_cast<uintptr_t>(desc->workspace) % 32 == 0, LEMOQ_ERR_INVALID,
+                  "step_create: workspace must be 32-byte aligned");
     for (int l = 0; l < desc->layers; ++l) {
         const lemoq_layer_desc& L = layers[l];
         LEMOQ_REQUIRE(L.ln1 && L.ln2 && L.q_norm && L.k_norm && L.qkv_codes && L.qkv_scale && L.o_codes && L.o_scale &&
