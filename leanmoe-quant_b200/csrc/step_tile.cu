@@ -1341,9 +1341,9 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 grid_wait();
                 prepare_attention_output(p, S);
             } else if (ph == 0) {
-                prepare(p.eps, embed_row, l == 0 ? nullptr : f_xin, tag - 1, 1, L.ln1, p.H, p.H >> 7, S.xplanes, S.xsx, nullptr, S.red, p.err_flag);
+                prepare(p.eps, embed_row, l == 0 ? nullptr : f_xin, tag - 1, 2, L.ln1, p.H, p.H >> 7, S.xplanes, S.xsx, nullptr, S.red, p.err_flag);
             } else if (ph == 3) {
-                prepare(p.eps, nullptr, f_xa, tag, 1, L.ln2, p.H, p.H >> 7, S.xplanes, S.xsx, S.xh, S.red, p.err_flag);
+                prepare(p.eps, nullptr, f_xa, tag, 2, L.ln2, p.H, p.H >> 7, S.xplanes, S.xsx, S.xh, S.red, p.err_flag);
             } else {
                 prepare(p.eps, nullptr, f_act, tag, 2, nullptr, p.F, (p.K * p.F) >> 7, S.big, fsx, nullptr, S.red, p.err_flag);
             }
@@ -1356,7 +1356,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     __half resid = __float2half_rn(0.f);
                     if (ph == 2) {  // the residual of this lane's row (this block has seen the tag of every word in phase A)
                         const int n = tg * 8 + g;
-                        resid = l == 0 ? embed_row[n] : __ushort_as_half(static_cast<unsigned short>(flag_load(f_xin + n) & 0xffffu));
+                        resid = l == 0 ? embed_row[n] : __ushort_as_half(static_cast<unsigned short>((flag_load(f_xin + (n >> 1)) >> (16 * (n & 1))) & 0xffffu));
                     }
                     if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
                     c_par ^= 1u;
@@ -1406,7 +1406,10 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                             }
                         }
                     } else if (ph == 2) {
-                        if (t == 0) flag_store(f_xa + tg * 8 + g, __half_as_ushort(__hadd(__float2half_rn(val), resid)), tag);
+                        // the residual stream travels two values per word: rows g and g + 1 of the tile meet in the even row's lane
+                        const uint32_t mine = __half_as_ushort(__hadd(__float2half_rn(val), resid));
+                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 4);
+                        if (t == 0 && (g & 1) == 0) flag_store(f_xa + ((tg * 8 + g) >> 1), mine | (next << 16), tag);
                     } else if (ph == 3) {
                         const int e = tg * 4 + g;
                         if (t == 0 && g < 4 && e < p.E) {
@@ -1428,15 +1431,22 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 const int nrows = geo.f_blocks * 8;
                 consumer_sync();
 #pragma unroll 1
-                for (int i = tid; i < nrows; i += kConsumerThreads) {
+                for (int i0 = 0; i0 < nrows; i0 += kConsumerThreads) {  // every thread makes every trip: the rows meet in pairs
+                    const int i = i0 + tid;
+                    const bool on = i < nrows;
                     const int j = i >> 3, r = i & 7;
-                    float out = 0.f;
-#pragma unroll 1
-                    for (int slot = 0; slot < p.K; ++slot) out = fmaf(S.route_w[slot], S.part[(j * p.K + slot) * 8 + r], out);
                     const int n = (b + j * G) * 8 + r;
-                    // the residual: this block has seen the tag of every word of the stream in the router phase
-                    const __half resid = __ushort_as_half(static_cast<unsigned short>(flag_load(f_xa + n) & 0xffffu));
-                    flag_store(f_x2 + n, __half_as_ushort(__hadd(__float2half_rn(out), resid)), tag);
+                    uint32_t mine = 0;
+                    if (on) {
+                        float out = 0.f;
+#pragma unroll 1
+                        for (int slot = 0; slot < p.K; ++slot) out = fmaf(S.route_w[slot], S.part[(j * p.K + slot) * 8 + r], out);
+                        // the residual: this block has seen the tag of every word of the stream in the router phase
+                        const __half resid = __ushort_as_half(static_cast<unsigned short>((flag_load(f_xa + (n >> 1)) >> (16 * (n & 1))) & 0xffffu));
+                        mine = __half_as_ushort(__hadd(__float2half_rn(out), resid));
+                    }
+                    const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);  // row n + 1: the neighbouring thread
+                    if (on && (r & 1) == 0) flag_store(f_x2 + (n >> 1), mine | (next << 16), tag);
                 }
             } else if (ph == 0) {
                 if (!last) {
