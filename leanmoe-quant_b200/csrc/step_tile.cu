@@ -62,7 +62,8 @@ constexpr int kWarps = kStreamWarps;    // warps that take part in the block-wid
 constexpr int kConsumerThreads = kStreamWarps * 32;
 constexpr int kThreads = (kStreamWarps + kProducerWarps) * 32;
 constexpr int kPad = 64;                // plane segments and vector quarters sit 64 bytes off their natural stride
-constexpr int kScaleOff = 8 * 2048;     // the group scales of a tile sit behind its rows
+constexpr int kRunPad = 64;             // every run of four code rows of a tile sits this much further than the one before
+constexpr int kScaleOff = 8 * 2048 + 256;  // the group scales of a tile sit behind its rows (at most four runs)
 constexpr int kStageBytes = kScaleOff + 256;
 constexpr int kKvTile = 64;             // cached positions per attention tile
 constexpr int kMaxLayers = 33;
@@ -296,13 +297,14 @@ __device__ __forceinline__ float tile_s8_steps(const unsigned char* alo, const u
     return acc;
 }
 
-// One int8 tile: 8 rows of K codes in a stage (row stride K) against the plane segments of a vector.
-// bp: this lane's segment pointer (+ t*16 applied here).  sx: the K/128 group scales of the vector.  sc: the
-// K/128 fp16 group scales of row g.  Returns the lane's share of row g (to be added over the 4 lanes of a group).
-__device__ __forceinline__ float tile_s8(const unsigned char* st, int K, int g, int t, const unsigned char* bp, const float* sx,
+// One int8 tile: 8 rows of K codes in a stage (tile row r at r * K + (r >> 2) * kRunPad) against the plane segments
+// of a vector.  r: the tile row of this lane's instruction row (tile_row()).  bp: this lane's segment pointer (+ t*16
+// applied here).  sx: the K/128 group scales of the vector.  sc: the K/128 fp16 group scales of row r.  Returns the
+// lane's share of row r (to be added over the 4 lanes of a group).
+__device__ __forceinline__ float tile_s8(const unsigned char* st, int K, int r, int t, const unsigned char* bp, const float* sx,
                                          const __half* sc, const float (&pw)[4]) {
     const int half_k = K >> 1, gh = K >> 8;  // bytes per half row, groups per half
-    const unsigned char* alo = st + g * K + t * 16;
+    const unsigned char* alo = st + r * K + (r >> 2) * kRunPad + t * 16;
     const unsigned char* ahi = alo + half_k;
     bp += t * 16;
     float acc = 0.f;
@@ -382,7 +384,7 @@ struct Geo {
     int h, split;   // this block's (head, split) unit
     int tile0;      // first KV tile of this block's slice
     int owner;      // the slice contains the new token: this block writes its K/V row
-    int kvt;        // cached positions per KV tile: 64 (int8 codes) or 32 (fp16 values); 8 KB of keys + 8 KB of values either way
+    int kvt;        // cached positions per KV tile: 16, 32 or 64 (int8 codes, chosen per step) or 32 (fp16 values)
     int kv16;       // the cache is read as fp16 (no int8 mirror)
     int has_unit;   // this block has a unit at all
     int nt[8];      // tiles of this block per kind (index 6: the lm_head tiles)
@@ -444,46 +446,56 @@ __device__ __noinline__ void issue_tile(const Smem& S, int layer, int kind, int 
             bytes = tx;
         }
     } else {
-        // rows of a tile are consecutive in memory (gate/up: two runs of 4): lane 0 (and 1) copy the codes, lane 2 (and 3) the scales
+        // The code rows of a tile land in runs of four, each run 64 bytes further than its natural place (tile row r at
+        // r * K + (r >> 2) * 64): the eight lanes that read 16 bytes each of tile rows r and r + 4 in one request then
+        // hit different banks.  Lanes 0-3 copy one run of codes each, lanes 4-5 the group scales (rows of a run are
+        // consecutive in memory; gate/up: the gate run and the up run; down: the runs of one routed expert or of two).
         const int tg = geo.b + lt * geo.G;
-        uint32_t K = geo.H, row0;    // row width, first row of this lane's run
-        uint32_t rows = 8, at = 0;   // rows of this lane's run and where they land (in rows)
-        bool two = false;            // the tile has a second run (lanes 1 and 3)
+        const uint32_t run = lane & 3, half = lane & 1;  // code lanes: run of four rows; scale lanes 4, 5: first / second part
+        uint32_t K = geo.H;          // row width
+        uint32_t crow = 0, srow = 0; // first row of this lane's run of codes / part of the scales
+        uint32_t nruns = 2;          // runs of four code rows in the tile
+        uint32_t sparts = 1, srows = 8;  // parts of the scales and rows per part
         const char* cbase;
         const char* sbase;
         if (kind == KE) {  // 4 gate rows + 4 up rows of one routed expert
             const int slot = tg >> geo.shF4, n0 = (tg - (slot << geo.shF4)) * 4;
-            row0 = static_cast<uint32_t>(S.route_id[slot]) * 2 * geo.F + n0 + (lane & 1 ? geo.F : 0);
-            rows = 4;
-            at = (lane & 1) * 4;
-            two = true;
+            crow = srow = static_cast<uint32_t>(S.route_id[slot]) * 2 * geo.F + n0 + (half ? geo.F : 0);
+            sparts = 2;
+            srows = 4;
             cbase = reinterpret_cast<const char*>(L.gu_codes);
             sbase = reinterpret_cast<const char*>(L.gu_scale);
-        } else if (kind == KF) {  // 8 down rows of one routed expert, or of two (odd lanes: the second one)
+        } else if (kind == KF) {  // 8 down rows of one routed expert, or of two (runs 2-3 and scale part 1: the second one)
             const int j = udiv_small(lt, geo.f_magic), pp = lt - j * geo.ftiles;
-            const int slot = geo.fpair ? 2 * pp + (lane & 1) : pp;
-            two = geo.fpair && 2 * pp + 1 < geo.K;
-            row0 = static_cast<uint32_t>(S.route_id[min(slot, geo.K - 1)]) * geo.H + (geo.b + j * geo.G) * 8;
-            at = geo.fpair ? (lane & 1) * 8 : 0;
+            const bool two = geo.fpair && 2 * pp + 1 < geo.K;
+            const uint32_t first = (geo.b + j * geo.G) * 8;
+            const int cslot = geo.fpair ? 2 * pp + static_cast<int>(run >> 1) : pp, sslot = geo.fpair ? 2 * pp + static_cast<int>(half) : pp;
+            crow = static_cast<uint32_t>(S.route_id[min(cslot, geo.K - 1)]) * geo.H + first + (run & 1) * 4;
+            srow = static_cast<uint32_t>(S.route_id[min(sslot, geo.K - 1)]) * geo.H + first;
+            nruns = two ? 4 : 2;
+            sparts = two ? 2 : 1;
             K = geo.F;
             cbase = reinterpret_cast<const char*>(L.dn_codes);
             sbase = reinterpret_cast<const char*>(L.dn_scale);
         } else {  // 8 consecutive rows of q.k.v / lm_head (KA) or o_proj (KC)
-            row0 = tg * 8;
+            crow = tg * 8 + run * 4;
+            srow = tg * 8;
             K = kind == KA ? geo.H : geo.A;
             cbase = reinterpret_cast<const char*>(kind == KA ? L.qkv_codes : L.o_codes);
             sbase = reinterpret_cast<const char*>(kind == KA ? L.qkv_scale : L.o_scale);
         }
         const uint32_t sb = (K >> 7) * 2;  // bytes of one row of group scales
-        tx = (kind == KF && two ? 16u : 8u) * (K + sb);
-        if (lane == 0 || (lane == 1 && two)) {
-            src = cbase + static_cast<size_t>(row0) * K;
-            bytes = rows * K;
-            dst = at * K;
-        } else if (lane == 2 || (lane == 3 && two)) {
-            src = sbase + static_cast<size_t>(row0) * sb;
-            bytes = rows * sb;
-            dst = kScaleOff + at * sb;
+        tx = nruns * 4u * (K + sb);
+        if (lane < 4) {
+            if (run < nruns) {
+                src = cbase + static_cast<size_t>(crow) * K;
+                bytes = 4 * K;
+                dst = run * (4 * K + kRunPad);
+            }
+        } else if (lane < 6 && half < sparts) {
+            src = sbase + static_cast<size_t>(srow) * sb;
+            bytes = srows * sb;
+            dst = kScaleOff + half * srows * sb;
         }
     }
     if (lane == 0) mbar_expect_tx(bar, tx);
@@ -933,11 +945,13 @@ __device__ __noinline__ void attention_prologue(const StepParams& p, const StepL
     consumer_sync();
 }
 
-// One KV tile (64 positions in a stage) of the warp: scores through the int8 dot product against the planes of q
-// (instruction rows = positions), online softmax (base 2), values with each lane owning four output dimensions.
+// One KV tile (T = 16, 32 or 64 positions in a stage: keys at its start, values 8 KB further) of the warp: scores
+// through the int8 dot product against the planes of q (instruction rows = positions), online softmax (base 2),
+// values with each lane owning four output dimensions.
+template <int T>
 __device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, const Geo& geo, int lt, int lane, int warp, const float (&pw)[4],
                                                const float (&kscale)[2], const float (&vscale)[2], float& m_i, float& l_i, float (&acc)[4]) {
-    constexpr int D = kHeadDim, T = kKvTile;
+    constexpr int D = kHeadDim, VO = kKvTile * kHeadDim;  // VO: where the values start
     const int g = lane >> 2, t = lane & 3;
     const int base = (geo.tile0 + lt) * T;
     const int nvalid = min(T, geo.nf - base);
@@ -945,11 +959,11 @@ __device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, co
         // the row of the new token: the codes this block has just derived (the copy may have read the slot before the write)
         const int row = geo.pos - base;
         reinterpret_cast<uint32_t*>(st + row * D)[lane] = sm.newk[lane];
-        reinterpret_cast<uint32_t*>(st + T * D + row * D)[lane] = sm.newv[lane];
+        reinterpret_cast<uint32_t*>(st + VO + row * D)[lane] = sm.newv[lane];
         __syncwarp();
     }
     // kscale[r] / vscale[r] of this lane belong to position 32 r + lane of the tile
-    auto scale_of = [&](const float (&sc)[2], int pi) { return __shfl_sync(0xffffffffu, pi < 32 ? sc[0] : sc[1], pi & 31); };
+    auto scale_of = [&](const float (&sc)[2], int pi) { return __shfl_sync(0xffffffffu, (T <= 32 || pi < 32) ? sc[0] : sc[1], pi & 31); };
     const unsigned char* qp = sm.qplanes + (g < 3 ? g : (g & 1)) * kQPlaneStride + t * 16;
     const float qsx = sm.qsx;
     float s[T / 8];
@@ -1017,7 +1031,7 @@ __device__ __forceinline__ void attention_tile(unsigned char* st, AttnSm& sm, co
         }
     }
     __syncwarp();
-    const unsigned char* vrow = st + T * D + lane * 4;
+    const unsigned char* vrow = st + VO + lane * 4;
     const uint32_t* pq = reinterpret_cast<const uint32_t*>(sm.pq[warp]);
     int ai[4] = {0, 0, 0, 0};
 #pragma unroll 4
@@ -1141,6 +1155,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
     Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int gr = (g >> 1) + 4 * (g & 1);  // int8 weight tiles: the tile row of instruction row g (rows r and r + 4 are neighbours)
     const int G = gridDim.x, b = blockIdx.x;
     const int A = p.heads * p.D;
     {
@@ -1180,7 +1195,13 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
             const bool has_unit = b < p.heads * p.splits;
             const int unit = has_unit ? b : 0;
             geo.kv16 = p.kv_int8 ? 0 : 1;
-            geo.kvt = p.kv_int8 ? kKvTile : kKvTile / 2;
+            // int8 codes: the smallest tile of 16, 32 or 64 positions with which no warp of a unit gets a second tile (a tile
+            // is one warp's serial work, so short contexts are cut finer); fp16 values: 32 positions (8 KB of keys)
+            geo.kvt = kKvTile / 2;
+            if (p.kv_int8) {
+                geo.kvt = 16;
+                while (geo.kvt < kKvTile && ((nf + geo.kvt - 1) / geo.kvt + p.splits - 1) / p.splits > kStreamWarps) geo.kvt *= 2;
+            }
             const int ntile_total = (nf + geo.kvt - 1) / geo.kvt;
             const int tps = (ntile_total + p.splits - 1) / p.splits;
             geo.h = unit / p.splits;
@@ -1296,8 +1317,8 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         float kscale[2], vscale[2];
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
-                            const int pos = (geo.tile0 + lt) * kKvTile + 32 * r + lane;
-                            const bool in = pos < geo.nf;
+                            const int pos = (geo.tile0 + lt) * geo.kvt + 32 * r + lane;
+                            const bool in = 32 * r + lane < geo.kvt && pos < geo.nf;
                             const int64_t at = static_cast<int64_t>(geo.h) * geo.S + (in ? pos : 0);
                             const bool fresh = geo.owner && pos == geo.pos;  // the new token: the scales this block has just derived
                             kscale[r] = fresh ? __half2float(__ushort_as_half(sm.newks)) : (in ? __half2float(__ldcg(L.ks + at)) : 0.f);
@@ -1305,7 +1326,9 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         }
                         if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
                         c_par ^= 1u;
-                        attention_tile(my_stage, sm, geo, lt, lane, warp, pw1v, kscale, vscale, m_i, l_i, acc);
+                        if (geo.kvt == 16) attention_tile<16>(my_stage, sm, geo, lt, lane, warp, pw1v, kscale, vscale, m_i, l_i, acc);
+                        else if (geo.kvt == 32) attention_tile<32>(my_stage, sm, geo, lt, lane, warp, pw1v, kscale, vscale, m_i, l_i, acc);
+                        else attention_tile<kKvTile>(my_stage, sm, geo, lt, lane, warp, pw1v, kscale, vscale, m_i, l_i, acc);
                         stage_release(empty_bar);
                     }
                     *reinterpret_cast<float4*>(&sm.wacc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -1341,6 +1364,20 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                 grid_wait();
                 prepare_attention_output(p, S);
             } else if (ph == 0) {
+                if (!last && geo.has_unit && !geo.kv16) {
+                    // the scales of this warp's first KV tile of the coming attention phase, towards the L2 cache
+                    const int ltb = warp - cbase + (warp < cbase ? kStreamWarps : 0);
+                    const int pos = (geo.tile0 + ltb) * geo.kvt + lane;
+                    if (ltb < geo.nt[KB] && lane < geo.kvt && pos < geo.nf) {
+                        const int64_t at = static_cast<int64_t>(geo.h) * geo.S + pos;
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.ks + at));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(L.vs + at));
+                        if (geo.kvt > 32 && pos + 32 < geo.nf) {
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.ks + at + 32));
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(L.vs + at + 32));
+                        }
+                    }
+                }
                 prepare(p.eps, embed_row, l == 0 ? nullptr : f_xin, tag - 1, 2, L.ln1, p.H, p.H >> 7, S.xplanes, S.xsx, nullptr, S.red, p.err_flag);
             } else if (ph == 3) {
                 prepare(p.eps, nullptr, f_xa, tag, 2, L.ln2, p.H, p.H >> 7, S.xplanes, S.xsx, S.xh, S.red, p.err_flag);
@@ -1355,7 +1392,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                     const int tg = b + lt * G;  // global tile index (not in the down phase)
                     __half resid = __float2half_rn(0.f);
                     if (ph == 2) {  // the residual of this lane's row (this block has seen the tag of every word in phase A)
-                        const int n = tg * 8 + g;
+                        const int n = tg * 8 + gr;
                         resid = l == 0 ? embed_row[n] : __ushort_as_half(static_cast<unsigned short>((flag_load(f_xin + (n >> 1)) >> (16 * (n & 1))) & 0xffffu));
                     }
                     if (!stage_acquire(full_bar, c_par, p.err_flag)) break;
@@ -1369,27 +1406,27 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                         // one or two routed experts' rows of the same 8 outputs: each against its own activation planes
                         const int j = udiv_small(lt, geo.f_magic), pp = lt - j * geo.ftiles;
                         const int seg = (K >> 1) + kPad, slot = geo.fpair ? 2 * pp : pp;
-                        const __half* sc = reinterpret_cast<const __half*>(my_stage + kScaleOff) + g * (K >> 7);
-                        val = tile_s8(my_stage, K, g, t, S.big + slot * 6 * seg + bseg * seg, fsx + slot * (K >> 7), sc, pw2v);
+                        const __half* sc = reinterpret_cast<const __half*>(my_stage + kScaleOff) + gr * (K >> 7);
+                        val = tile_s8(my_stage, K, gr, t, S.big + slot * 6 * seg + bseg * seg, fsx + slot * (K >> 7), sc, pw2v);
                         val += __shfl_xor_sync(0xffffffffu, val, 1);
                         val += __shfl_xor_sync(0xffffffffu, val, 2);
-                        if (t == 0) S.part[(j * p.K + slot) * 8 + g] = val;
-                        if (geo.fpair && slot + 1 < p.K) {
-                            val = tile_s8(my_stage + 8 * K, K, g, t, S.big + (slot + 1) * 6 * seg + bseg * seg, fsx + (slot + 1) * (K >> 7),
+                        if (t == 0) S.part[(j * p.K + slot) * 8 + gr] = val;
+                        if (geo.fpair && slot + 1 < p.K) {  // tile rows 8-15: two runs further
+                            val = tile_s8(my_stage + 8 * K + 2 * kRunPad, K, gr, t, S.big + (slot + 1) * 6 * seg + bseg * seg, fsx + (slot + 1) * (K >> 7),
                                           sc + 8 * (K >> 7), pw2v);
                             val += __shfl_xor_sync(0xffffffffu, val, 1);
                             val += __shfl_xor_sync(0xffffffffu, val, 2);
-                            if (t == 0) S.part[(j * p.K + slot + 1) * 8 + g] = val;
+                            if (t == 0) S.part[(j * p.K + slot + 1) * 8 + gr] = val;
                         }
                     } else {
-                        val = tile_s8(my_stage, K, g, t, S.xplanes + bseg * ((K >> 1) + kPad), S.xsx,
-                                      reinterpret_cast<const __half*>(my_stage + kScaleOff) + g * (K >> 7), pw2v);
+                        val = tile_s8(my_stage, K, gr, t, S.xplanes + bseg * ((K >> 1) + kPad), S.xsx,
+                                      reinterpret_cast<const __half*>(my_stage + kScaleOff) + gr * (K >> 7), pw2v);
                         val += __shfl_xor_sync(0xffffffffu, val, 1);
                         val += __shfl_xor_sync(0xffffffffu, val, 2);
                     }
                     stage_release(empty_bar);
                     if (ph == 0) {
-                        const int n = tg * 8 + g;
+                        const int n = tg * 8 + gr;
                         const __half hv = __float2half_rn(val);
                         const float f = __half2float(hv);
                         if (t == 0) {
@@ -1406,10 +1443,11 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                             }
                         }
                     } else if (ph == 2) {
-                        // the residual stream travels two values per word: rows g and g + 1 of the tile meet in the even row's lane
+                        // the residual stream travels two values per word: tile rows r and r + 1 meet in the even row's lane
+                        // (the lanes of tile row r + 1 are those of instruction row g + 2)
                         const uint32_t mine = __half_as_ushort(__hadd(__float2half_rn(val), resid));
-                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 4);
-                        if (t == 0 && (g & 1) == 0) flag_store(f_xa + ((tg * 8 + g) >> 1), mine | (next << 16), tag);
+                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 8);
+                        if (t == 0 && (gr & 1) == 0) flag_store(f_xa + ((tg * 8 + gr) >> 1), mine | (next << 16), tag);
                     } else if (ph == 3) {
                         const int e = tg * 4 + g;
                         if (t == 0 && g < 4 && e < p.E) {
@@ -1418,11 +1456,11 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
                             p.router_logits[static_cast<int64_t>(l) * p.E + e] = hv;  // kept for inspection
                         }
                     } else if (ph == 4) {
-                        const float up = __shfl_down_sync(0xffffffffu, val, 16);  // rows 4-7 of the tile are the up rows
+                        const float up = __shfl_down_sync(0xffffffffu, val, 4);  // tile rows 4-7 are the up rows: the next instruction row
                         const uint32_t mine = __half_as_ushort(__float2half_rn(val * (1.0f / (1.0f + expf(-val))) * up));
-                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 4);  // the activation of the next row
-                        const int slot = tg >> geo.shF4, n = ((tg - (slot << geo.shF4)) << 2) + g;
-                        if (t == 0 && (g == 0 || g == 2)) flag_store(f_act + ((slot * p.F + n) >> 1), mine | (next << 16), tag);  // two per word
+                        const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 8);  // the activation of the next tile row
+                        const int slot = tg >> geo.shF4, n = ((tg - (slot << geo.shF4)) << 2) + gr;
+                        if (t == 0 && (gr == 0 || gr == 2)) flag_store(f_act + ((slot * p.F + n) >> 1), mine | (next << 16), tag);  // two per word
                     }
                 }
             }
@@ -1552,6 +1590,7 @@ __global__ void __launch_bounds__(kThreads, 1) step_tile_kernel(const __grid_con
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
+static_assert(sizeof(tile::Smem) + 128 <= 227 * 1024, "the block's shared memory must fit one SM");
 size_t tile_smem_bytes() { return sizeof(tile::Smem) + 128; }
 
 int set_flag_spin_limit(int polls) {
@@ -1574,11 +1613,14 @@ bool tile_eligible(const lemoq_step_desc& d) {
 }
 
 // Attention splits per head for the tile form: every (head, split) unit should have at most one KV tile per
-// streaming warp.
+// streaming warp.  A tile is one warp's serial work and every further split makes the merge of the partials longer
+// (it takes the splits four at a time), so a short int8 cache is cut into tiles of 32 positions, about 8 per unit and
+// at most 6 splits, and a long one into tiles of 64, 10 per unit (measured at 1024 and 4096 cached positions).
 int tile_attention_splits(const lemoq_step_desc& d, int grid) {
-    const int kvt = d.kv_int8 ? tile::kKvTile : tile::kKvTile / 2;  // positions per 16 KB tile
-    const int tiles = (d.max_len + kvt - 1) / kvt;
-    int s = (tiles + tile::kStreamWarps - 1) / tile::kStreamWarps;
+    const int tiles64 = (d.max_len + tile::kKvTile - 1) / tile::kKvTile, tiles32 = (d.max_len + 31) / 32;
+    int s;
+    if (d.kv_int8 && tiles64 <= 30) s = std::min(6, (tiles32 + 7) / 8);
+    else s = ((d.kv_int8 ? tiles64 : tiles32) + tile::kStreamWarps - 1) / tile::kStreamWarps;
     s = std::max(1, std::min(s, tile::kMaxSplits));
     return std::max(1, std::min(s, grid / d.heads));
 }
