@@ -174,6 +174,9 @@ def time_oracle_steps(wq, st, first_token: int, ctx: int, steps: int, warmup: in
     return times
 
 
+REFERENCE_MAX_STEPS = 60
+
+
 def run_reference(args) -> int:
     """The reference arm: the CPU implementation of the decode step on the host cores."""
     import torch
@@ -187,17 +190,21 @@ def run_reference(args) -> int:
     torch.set_num_threads(cores)
     spec = glue.OlmoeSpec()
     steps, warmup = max(1, args.steps), max(1, args.warmup)
+    # a CPU step takes most of a second: at most 60 of the K steps (and 3 warm-up steps) are run, so that the arm ends
+    # within a minute or two whatever K is; the line says how many were timed
+    timed, warm = min(steps, REFERENCE_MAX_STEPS), min(warmup, 3)
     wq = synthetic_oracle_weights(spec)
-    st = glue.new_state(spec, args.ctx + steps + warmup)
+    st = glue.new_state(spec, args.ctx + timed + warm)
     g = torch.Generator().manual_seed(1)
     for i in range(spec.layers):
         st.keys[i][:, :, : args.ctx] = torch.randn(1, spec.heads, args.ctx, spec.head_dim, generator=g).half()
         st.values[i][:, :, : args.ctx] = torch.randn(1, spec.heads, args.ctx, spec.head_dim, generator=g).half()
     glue.build_int8_mirror(st)
-    times = time_oracle_steps(wq, st, 1, args.ctx, steps, warmup)
+    times = time_oracle_steps(wq, st, 1, args.ctx, timed, warm)
     ms = 1000.0 * sum(times) / len(times)
     value = 1000.0 / ms
-    sample = "%d decode steps of the 16-layer canonical model at ctx %d (synthetic int8 codes, random fp16 KV)" % (steps, args.ctx)
+    sample = "%d decode steps (of --steps %d; %d warm-up) of the 16-layer canonical model at ctx %d (synthetic int8 codes, random fp16 KV)" % (
+        timed, steps, warm, args.ctx)
     from benchmarks.bytes import CANONICAL_QUANT, ModelSpec, byte_budget
     from lemoq.model import OlmoeConfig
 
@@ -205,7 +212,7 @@ def run_reference(args) -> int:
     first = byte_budget(ModelSpec.from_config(OlmoeConfig()), args.ctx + 1, CANONICAL_QUANT, kv_int8=True)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": warmup, "steps_timed": timed, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 weights/KV, fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": workload_config(args.ctx, spec.layers, world, first["T"]),
         "run": {"weights": "synthetic int8 codes and fp16 scales of the canonical shapes (the work of a step does not depend on the values)",
@@ -441,6 +448,14 @@ def run_gpu(args) -> int:
     session.stream.synchronize()
     barrier()
     dev_ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+    # where the last timed step spent its time: block 0's time stamps at the phase boundaries of the whole-step kernel
+    phase_us = None
+    stamps = session.step_phase_times_us() if native else None
+    if stamps is not None:
+        rows = stamps["phases"][1:] if stamps["phases"].shape[0] > 1 else stamps["phases"]  # layer 0 starts cold
+        phase_us = {"order": ["q.k.v", "attention", "o_proj", "router", "gate_up", "down"],
+                    "per_layer_mean": [round(float(v), 2) for v in rows.mean(0)],
+                    "lm_head": round(float(stamps["lm_head"]), 2), "step": round(float(stamps["total"]), 2)}
     # ---------------- e2e: the public session API with host buffers ----------------
     # replay_chained(B): the first step's inputs come from pinned host memory (one 32-byte copy), B replays run with
     # no host work in between, the B token ids come back in one copy to pinned host memory; the host continues from
@@ -503,7 +518,7 @@ def run_gpu(args) -> int:
         "config": workload_config(ctx, model.config.num_hidden_layers, world, byte_budget(spec, ctx + 1, CANONICAL_QUANT, kv_int8=True)["T"]),
         "run": {"engine": session.capture_info.get("engine"), "step_kernel": session.capture_info.get("step_kernel"),
                 "pdl": session.capture_info.get("pdl"), "weights": "random-init N(0,0.02) seed 0, RTN-quantised on the GPU",
-                "execution": "one CUDA graph per step", "prefill_ms": round(prefill_ms, 1)},
+                "execution": "one CUDA graph per step", "prefill_ms": round(prefill_ms, 1), "phase_us": phase_us},
         "ms_per_token": dev_ms, "bytes_per_step": budget["T"], "byte_floor_ms": floor_ms,
         "floor_fraction": floor_ms / dev_ms, "floor_fraction_e2e": floor_ms / e2e_ms,
         "e2e": {"value": world * 1000.0 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms,
