@@ -2,10 +2,10 @@
 // int8 tensor-core dot product.
 //
 // One block per SM stays resident for the whole step.  All weights move as TILES: 8 whole rows and the rows'
-// group scales, brought into a 16.6 KB shared-memory stage by two to four bulk asynchronous copies, each issued by
-// a lane of its own (the rows of a tile are adjacent in memory, so their codes are one run of bytes and their
-// scales another; an expert's 4 gate + 4 up rows, and a down tile that holds rows of two routed experts, are two
-// runs each).  The block has ten stages.  Ten CONSUMER warps own one stage
+// group scales, brought into a 16.9 KB shared-memory stage by three to six bulk asynchronous copies, each issued by
+// a lane of its own: the codes in runs of four rows (adjacent in memory; every run lands 64 bytes further than its
+// natural place, so that the 16-byte reads of rows r and r + 4, which one request of a quarter warp combines, hit
+// different banks), the scales in one or two runs.  The block has ten stages.  Ten CONSUMER warps own one stage
 // each and do all the arithmetic; five PRODUCER warps do nothing but issue copies: each keeps two stages filled,
 // walking the block's tile sequence of the WHOLE STEP in order (a copy instruction occupies the issuing warp for
 // well over a thousand cycles, which is why the consumers do not issue their own).  A stage is handed back and
@@ -21,9 +21,9 @@
 // Arithmetic: the activation vector of a phase is turned once per block into three planes of signed
 // 7-bit digits with one power-of-two scale per group of 128 (x = sx * (d2*2^14 + d1*2^7 + d0)).  The
 // planes are the B operand of mma.sync m16n8k32 s8, the int8 weight codes are the A operand as they
-// sit in memory.  The 16 rows of the instruction are the 8 rows of the tile, twice: rows 0-7 take the
-// first half of k, rows 8-15 the second half, and B carries the planes of the first half in columns
-// 0-2 and those of the second half in columns 3-5.  One instruction thus multiplies 8 rows x 64 codes;
+// sit in memory.  The 16 rows of the instruction are the 8 rows of the tile, twice (instruction row g is tile row
+// g/2 + 4 (g mod 2)): rows 0-7 take the first half of k, rows 8-15 the second half, and B carries the planes of
+// the first half in columns 0-2 and those of the second half in columns 3-5.  One instruction thus multiplies 8 rows x 64 codes;
 // the int32 sums of a 128-group are exact and are scaled by (row scale x sx) in fp32.  The bytes a
 // lane loads for A and B are a permutation of k inside a 64-byte chunk, the same on both sides, so
 // 128-bit shared loads feed the fragments directly.  The router rows (fp16) go through mma.sync
@@ -37,8 +37,8 @@
 //
 // Phases per layer (what a block waits for -> what it publishes):
 //   A  q.k.v tiles          flagged x of the layer before; planes of RMSNorm(x)   -> flagged qkv + sum-of-squares partials
-//   B  attention            flagged qkv; one (head, split) per block, KV tiles of 64 positions through the same
-//                           stages; q/k norm + RoPE + KV row write fused          -> (m, l, acc) partial per unit
+//   B  attention            flagged qkv; one (head, split) per block, KV tiles of 16, 32 or 64 positions through the
+//                           same stages; q/k norm + RoPE + KV row write fused     -> (m, l, acc) partial per unit
 //      grid barrier
 //   C  o_proj tiles         splits of each head merged while the planes are built; + residual -> flagged x1
 //   D  router tiles (fp16)  flagged x1; planes of h2 = RMSNorm(x1) stay in shared memory for E -> flagged logits
