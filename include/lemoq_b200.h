@@ -321,7 +321,7 @@ typedef struct lemoq_step_desc {
     float eps;
     int norm_topk_prob;
     int kv_int8;            /* 1: attention reads the int8 mirror; 0: the fp16 cache       */
-    int attn_splits;        /* 0 = choose from the SM count and max_len; > 0: at most this many */
+    int attn_splits;        /* 0 = choose from the SM count and max_len; > 0: this many (whole-step kernel: at most) */
     int use_pdl;            /* 1: programmatic dependent launch between the step's kernels  */
     const void* embed;      /* (vocab, hidden) fp16                                         */
     const void* final_norm; /* (hidden) fp16                                                */
