@@ -270,3 +270,46 @@ def test_quantize_model_classification_rules():
         SchemeSpec(dequant="bogus")
     with pytest.raises(NotImplementedError):
         SchemeSpec.from_flags("w4a16", 128)
+
+
+def test_reference_arm_times_a_bounded_number_of_cpu_steps(monkeypatch, capsys):
+    """`bench.py --impl reference`: whatever --steps says, at most REFERENCE_MAX_STEPS CPU decode steps (3 warm-up
+    steps) are run, the line keeps the K it was launched with and says how many steps were timed, and its `config`
+    is the one the GPU arm prints for the same context."""
+    import argparse
+    import json
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    seen = {}
+
+    def fake_steps(wq, st, tok, ctx, steps, warmup):
+        seen.update(steps=steps, warmup=warmup, capacity=int(st.keys[0].shape[2]))
+        return [0.5] * steps
+
+    monkeypatch.setattr(bench, "synthetic_oracle_weights", lambda spec: None)
+    monkeypatch.setattr(bench, "time_oracle_steps", fake_steps)
+    monkeypatch.delenv("RANK", raising=False)
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    assert bench.run_reference(argparse.Namespace(steps=400, warmup=5, ctx=64, gpus=1)) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert seen["steps"] == bench.REFERENCE_MAX_STEPS and seen["warmup"] == 3
+    assert seen["capacity"] >= 64 + seen["steps"] + seen["warmup"]
+    assert line["impl"] == "reference" and line["steps"] == 400 and line["steps_timed"] == bench.REFERENCE_MAX_STEPS
+    assert line["value"] == pytest.approx(2.0) and line["ms_per_step"] == pytest.approx(500.0)
+    assert line["e2e"]["value"] == line["value"] and line["cpu_baseline"]["kind"] == "port"
+    assert str(bench.REFERENCE_MAX_STEPS) in line["cpu_baseline"]["sample"]
+    from benchmarks.bytes import CANONICAL_QUANT, ModelSpec, byte_budget
+    from lemoq.model import OlmoeConfig
+
+    first = byte_budget(ModelSpec.from_config(OlmoeConfig()), 64 + 1, CANONICAL_QUANT, kv_int8=True)["T"]
+    assert line["config"] == bench.workload_config(64, 16, 1, first)
+    # a short run is not stretched
+    assert bench.run_reference(argparse.Namespace(steps=2, warmup=1, ctx=64, gpus=1)) == 0
+    assert seen["steps"] == 2 and seen["warmup"] == 1
+    # ranks other than 0 do no work
+    monkeypatch.setenv("RANK", "1")
+    seen.clear()
+    assert bench.run_reference(argparse.Namespace(steps=2, warmup=1, ctx=64, gpus=2)) == 0 and not seen
